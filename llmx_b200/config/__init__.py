@@ -3,5 +3,6 @@ from .base import ConfigError, ModelConfig, Rule, apply_rules, read_config_json
 from .qwen3 import Qwen3Config, YarnScaling
 from .buzetar import BuzetarConfig
 from .kisepel import KisepelConfig
+from .zamizen import ZamizenConfig
 
-__all__ = ["ConfigError", "ModelConfig", "Rule", "apply_rules", "read_config_json", "Qwen3Config", "YarnScaling", "BuzetarConfig", "KisepelConfig"]
+__all__ = ["ConfigError", "ModelConfig", "Rule", "apply_rules", "read_config_json", "Qwen3Config", "YarnScaling", "BuzetarConfig", "KisepelConfig", "ZamizenConfig"]

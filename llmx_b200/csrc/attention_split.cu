@@ -81,6 +81,125 @@ qk_write_kernel(const float* __restrict__ proj, int stride, const float* __restr
     }
 }
 
+// The general finishing of the rows of a q/k/v product, for designs that put more between the product and the attention:
+//   u = proj + bias                                   (bias may be null)
+//   y[t] = sum_j taps_w[c, j] u[t - taps + 1 + j]      a short causal filter per channel, zeros before the request's first
+//                                                     token; inputs of earlier steps come from the request's state slot,
+//                                                     which holds the last taps - 1 values of u ([taps - 1][channels] at
+//                                                     `conv_off`); the step's last ones go to the slot the step writes
+//   q, k: a norm per head (RMS over D, weights of D values or none) before the rotation (norm 1) or after it (norm 2),
+//         a rotation of pair i < rot_pairs by position * freq[i]: the pair is (i, i + rot_pairs), or with `neighbours`
+//         (2i, 2i + 1)
+//   q -> q_out, [k ; v] -> the row's cache slot (kv_heads 0: the rows hold queries only, another layer's keys are read)
+// One block per row, a warp per head; blocks beyond the rows write the requests' new filter inputs.
+struct QkvFinish {
+    const float* proj;
+    int stride;
+    const float* bias;
+    const float* taps_w;
+    int taps;
+    float* state;
+    long long slot_floats, conv_off;
+    const int *row_request, *row_start, *row_count, *history, *slot_in, *slot_out;
+    const float *q_weight, *k_weight;
+    int norm;
+    float eps;
+    const float* freq;
+    int rot_pairs, neighbours;
+    const int *positions, *slots;
+    int heads, kv_heads, D, V, page_size, rows;
+};
+
+template <typename QT, typename KVT>
+__global__ void __launch_bounds__(128)
+qkv_finish_kernel(QkvFinish a, QT* __restrict__ q_out, KVT* __restrict__ cache) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float stage[4][32 * MAX_PER_LANE];
+    const int keep = a.taps - 1;
+    const int D = a.D, V = a.V;
+    const int channels = (a.heads + a.kv_heads) * D + a.kv_heads * V;
+    if ((int)blockIdx.x >= a.rows) {
+        // The filter's inputs a later step needs: the last `keep` values of u of the request, from this step's rows or,
+        // when the step brings fewer, from the slot read (the slot written is another one).
+        const int r = blockIdx.x - a.rows;
+        const int n = a.row_count[r], a0 = a.row_start[r], hist = a.history[r];
+        if (n <= 0) return;
+        const float* old = a.state + (size_t)a.slot_in[r] * a.slot_floats + a.conv_off;
+        float* fresh = a.state + (size_t)a.slot_out[r] * a.slot_floats + a.conv_off;
+        for (int c = threadIdx.x; c < channels; c += blockDim.x)
+            for (int s = 0; s < keep; ++s) {
+                const int ii = n - keep + s;
+                float x = 0.0f;
+                if (ii >= 0) x = a.proj[(size_t)(a0 + ii) * a.stride + c] + (a.bias ? a.bias[c] : 0.0f);
+                else if (hist + ii >= 0) x = old[(size_t)(keep + ii) * channels + c];
+                fresh[(size_t)s * channels + c] = x;
+            }
+        return;
+    }
+    const int row = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int r = a.row_request[row];
+    const int first = a.row_start[r], i0 = row - first, hist = a.history[r];
+    const float* old = keep > 0 ? a.state + (size_t)a.slot_in[r] * a.slot_floats + a.conv_off : nullptr;
+    const float pos = (float)a.positions[row];
+    const int slot = a.slots ? a.slots[row] : -1;                  // rows of queries alone have no cache slot
+    auto filtered = [&](int c) -> float {
+        const float b = a.bias ? a.bias[c] : 0.0f;
+        if (a.taps_w == nullptr) return a.proj[(size_t)row * a.stride + c] + b;
+        float y = 0.0f;
+        for (int jt = 0; jt <= keep; ++jt) {
+            const int ii = i0 - keep + jt;
+            float x = 0.0f;
+            if (ii >= 0) x = a.proj[(size_t)(first + ii) * a.stride + c] + b;
+            else if (hist + ii >= 0) x = old[(size_t)(keep + ii) * channels + c];
+            y = fmaf(a.taps_w[(size_t)c * a.taps + jt], x, y);
+        }
+        return y;
+    };
+    float* st = stage[warp];
+    const int v_off = (a.heads + a.kv_heads) * D;
+    for (int item = warp; item < a.heads + a.kv_heads; item += warps) {
+        const bool is_q = item < a.heads;
+        if (!is_q && slot < 0) continue;                              // a row whose cache write is skipped
+        const float* w = is_q ? a.q_weight : a.k_weight;
+        for (int d = lane; d < D; d += 32) st[d] = filtered(item * D + d);
+        __syncwarp();
+        if (a.norm == 1) {
+            float ss = 0.0f;
+            for (int d = lane; d < D; d += 32) ss = fmaf(st[d], st[d], ss);
+            const float rr = 1.0f / sqrtf(warp_sum(ss) / (float)D + a.eps);
+            for (int d = lane; d < D; d += 32) st[d] = st[d] * rr * (w ? w[d] : 1.0f);
+            __syncwarp();
+        }
+        for (int i = lane; i < a.rot_pairs; i += 32) {
+            const int ia = a.neighbours ? 2 * i : i, ib = a.neighbours ? 2 * i + 1 : i + a.rot_pairs;
+            const float u = st[ia], v = st[ib];
+            float sn, cs;
+            sincosf(pos * a.freq[i], &sn, &cs);
+            st[ia] = u * cs - v * sn;
+            st[ib] = v * cs + u * sn;
+        }
+        __syncwarp();
+        float rr = 1.0f;
+        if (a.norm == 2) {
+            float ss = 0.0f;
+            for (int d = lane; d < D; d += 32) ss = fmaf(st[d], st[d], ss);
+            rr = 1.0f / sqrtf(warp_sum(ss) / (float)D + a.eps);
+        }
+        if (is_q) {
+            QT* dst = q_out + ((size_t)row * a.heads + item) * D;
+            for (int d = lane; d < D; d += 32) dst[d] = from_float<QT>(a.norm == 2 ? st[d] * rr * (w ? w[d] : 1.0f) : st[d]);
+        } else {
+            const int g = item - a.heads;
+            KVT* dst = cache + (((size_t)(slot / a.page_size) * a.kv_heads + g) * a.page_size + slot % a.page_size) * (size_t)(D + V);
+            for (int d = lane; d < D; d += 32) dst[d] = from_float<KVT>(a.norm == 2 ? st[d] * rr * (w ? w[d] : 1.0f) : st[d]);
+            for (int d = lane; d < V; d += 32) dst[D + d] = from_float<KVT>(filtered(v_off + g * V + d));
+        }
+        __syncwarp();                                                 // the stage is written again for the warp's next head
+    }
+}
+
 template <typename QT, typename KVT>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_split_kernel(const QT* __restrict__ q, const KVT* __restrict__ cache, QT* __restrict__ out,
@@ -437,6 +556,39 @@ LLMX_EXPORT int llmx_qk_norm_rope_write(const float* proj, int stride, const flo
     else if (q_dtype == LLMX_F32 && cache_dtype == LLMX_F32) LLMX_QKW(float, float);
     else return LLMX_ERR_UNSUPPORTED;
 #undef LLMX_QKW
+    return launch_status();
+}
+
+// The general form of the above (see `QkvFinish`): proj float32 [rows, stride] = q (heads * D) | k (kv_heads * D) | v (kv_heads
+// * V), kv_heads 0 for rows of queries alone (then `cache` and `slots` are not used); bias float32 [channels] or null; taps_w
+// float32 [channels, taps] or null (taps 1: no filter); state float32 [slots, slot_floats] with the filter's inputs at
+// conv_off; norm 0 / 1 / 2 = none / before / after the rotation, q_weight and k_weight float32 [D] or null; freq float32
+// [rot_pairs]; the rows' requests, their row ranges, histories and the slots read and written as a step gives them.
+LLMX_EXPORT int llmx_qkv_finish(const float* proj, int stride, const float* bias, const float* taps_w, int taps, float* state,
+                                long long slot_floats, long long conv_off, const int* row_request, const int* row_start,
+                                const int* row_count, const int* history, const int* slot_in, const int* slot_out,
+                                const float* q_weight, const float* k_weight, int norm, float eps, const float* freq, int rot_pairs,
+                                int neighbours, const int* positions, const int* slots, void* q_out, int q_dtype, void* cache,
+                                int cache_dtype, int rows, int requests, int heads, int kv_heads, int D, int V, int page_size,
+                                cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (D <= 0 || V <= 0 || heads <= 0 || kv_heads < 0 || D > 32 * MAX_PER_LANE || 2 * rot_pairs > D || rot_pairs < 0 ||
+        (rot_pairs > 0 && freq == nullptr) || norm < 0 || norm > 2 || taps < 1 || (taps > 1 && (taps_w == nullptr || state == nullptr)) ||
+        (kv_heads > 0 && (cache == nullptr || slots == nullptr || page_size <= 0)))
+        return LLMX_ERR_BAD_ARGUMENT;
+    const long long channels = (long long)(heads + kv_heads) * D + (long long)kv_heads * V;
+    if (taps > 1 && conv_off + (taps - 1) * channels > slot_floats) return LLMX_ERR_BAD_ARGUMENT;
+    QkvFinish a{proj, stride, bias, taps_w, taps, state, slot_floats, conv_off, row_request, row_start, row_count, history, slot_in,
+                slot_out, q_weight, k_weight, norm, eps, freq, rot_pairs, neighbours, positions, slots, heads, kv_heads, D, V,
+                page_size > 0 ? page_size : 1, rows};
+    const dim3 grid(rows + (taps > 1 ? requests : 0));
+    const bool cache16 = kv_heads > 0 && cache_dtype == LLMX_BF16;
+    if (kv_heads > 0 && cache_dtype != LLMX_BF16 && cache_dtype != LLMX_F32) return LLMX_ERR_UNSUPPORTED;
+    if (q_dtype == LLMX_BF16 && cache16) launch_kernel(qkv_finish_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(128), 0, stream, a, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache);
+    else if (q_dtype == LLMX_BF16) launch_kernel(qkv_finish_kernel<__nv_bfloat16, float>, grid, dim3(128), 0, stream, a, (__nv_bfloat16*)q_out, (float*)cache);
+    else if (q_dtype == LLMX_F32 && cache16) launch_kernel(qkv_finish_kernel<float, __nv_bfloat16>, grid, dim3(128), 0, stream, a, (float*)q_out, (__nv_bfloat16*)cache);
+    else if (q_dtype == LLMX_F32) launch_kernel(qkv_finish_kernel<float, float>, grid, dim3(128), 0, stream, a, (float*)q_out, (float*)cache);
+    else return LLMX_ERR_UNSUPPORTED;
     return launch_status();
 }
 

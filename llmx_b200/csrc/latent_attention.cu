@@ -13,8 +13,10 @@
 // softmax over the row's keys lo..p (lo = max(0, p - window + 1), window <= 0: all), warps taking every fourth key
 // in increasing order and merged in warp order, then the value map.  Scores, weights and sums are 32-bit.
 //
-// Rotation: pairs (2i, 2i + 1), i < dims / 2, of the rotated part turn by angle p * f_i, f_i = base^(-2i / dims), given
-// as a float table; the angle is the float product, its cosine and sine the precise functions.
+// Rotation: pair i < dims / 2 of the rotated part turns by angle p * f_i, the frequencies f_i given as a float table
+// (base^(-2i / dims), or whatever blend of scaled frequencies the design asks for); the angle is the float product, its
+// cosine and sine the precise functions, both times `rot_mag` (a design's factor on rotated parts; 1 for none).  The
+// pair's members are neighbours (2i, 2i + 1), or with `rot_halves` the two halves' values (i, i + dims / 2).
 #include "common.cuh"
 #include "attn_common.cuh"
 #include <math.h>
@@ -22,15 +24,19 @@
 namespace {
 constexpr int WARPS = 4;
 
+// Where the two members of rotation pair i lie in a part whose first 2 * pairs values are rotated.
+__device__ __forceinline__ int pair_first(int i, int pairs, int halves) { return halves ? i : 2 * i; }
+__device__ __forceinline__ int pair_second(int i, int pairs, int halves) { return halves ? i + pairs : 2 * i + 1; }
+
 // A row of the stacked down projections is [query latent (Q) | key/value latent (C) | rotated key part (R)].  One block
 // per row: the query latent's RMS norm (weight wq) goes to `cq` in the type the next product reads; the key/value
 // latent's RMS norm (weight w) and the rotated part go to the row's cache slot (skipped when the slot is negative).
 template <typename KVT, typename QT>
 __global__ void __launch_bounds__(128)
 latent_write_kernel(const float* __restrict__ down, int stride, int Q, const float* __restrict__ wq, QT* __restrict__ cq,
-                    const float* __restrict__ w, float eps, const float* __restrict__ freq, int rot_pairs,
-                    const int* __restrict__ positions, const int* __restrict__ slots, KVT* __restrict__ cache, int C,
-                    int R) {
+                    const float* __restrict__ w, float eps, const float* __restrict__ freq, int rot_pairs, int rot_halves,
+                    float rot_mag, const int* __restrict__ positions, const int* __restrict__ slots, KVT* __restrict__ cache,
+                    int C, int R) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[32];
@@ -51,19 +57,17 @@ latent_write_kernel(const float* __restrict__ down, int stride, int Q, const flo
     const float rr = 1.0f / sqrtf(block_sum(s, scratch) / (float)C + eps);
     for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = from_float<KVT>(src[i] * rr * w[i]);
     const float p = (float)positions[row];
-    for (int i = threadIdx.x; i < R / 2; i += blockDim.x) {
-        const float a = src[C + 2 * i], b = src[C + 2 * i + 1];
-        if (i < rot_pairs) {
-            float sn, cs;
-            sincosf(p * freq[i], &sn, &cs);
-            dst[C + 2 * i] = from_float<KVT>(a * cs - b * sn);
-            dst[C + 2 * i + 1] = from_float<KVT>(b * cs + a * sn);
-        } else {
-            dst[C + 2 * i] = from_float<KVT>(a);
-            dst[C + 2 * i + 1] = from_float<KVT>(b);
-        }
+    for (int i = threadIdx.x; i < rot_pairs; i += blockDim.x) {
+        const int ia = C + pair_first(i, rot_pairs, rot_halves), ib = C + pair_second(i, rot_pairs, rot_halves);
+        const float a = src[ia], b = src[ib];
+        float sn, cs;
+        sincosf(p * freq[i], &sn, &cs);
+        sn *= rot_mag;
+        cs *= rot_mag;
+        dst[ia] = from_float<KVT>(a * cs - b * sn);
+        dst[ib] = from_float<KVT>(b * cs + a * sn);
     }
-    if ((R & 1) && threadIdx.x == 0) dst[C + R - 1] = from_float<KVT>(src[C + R - 1]);
+    for (int i = 2 * rot_pairs + threadIdx.x; i < R; i += blockDim.x) dst[C + i] = from_float<KVT>(src[C + i]);
 }
 
 // PL: values of a cache row a lane holds (C + R <= 32 * PL).
@@ -71,7 +75,8 @@ template <typename WT, typename KVT, int PL>
 __global__ void __launch_bounds__(WARPS * 32)
 latent_attention_kernel(const float* __restrict__ q, int q_stride, const KVT* __restrict__ cache,
                         const WT* __restrict__ w_uk, const WT* __restrict__ w_uv, WT* __restrict__ out,
-                        const float* __restrict__ freq, int rot_pairs, const int* __restrict__ row_request,
+                        const float* __restrict__ freq, int rot_pairs, int rot_halves, float rot_mag,
+                        const int* __restrict__ row_request,
                         const int* __restrict__ positions, const int* __restrict__ block_tables, int table_stride,
                         int heads, int D, int R, int V, int C, int page_size, int window, float scale) {
     pdl_trigger();
@@ -90,19 +95,17 @@ latent_attention_kernel(const float* __restrict__ q, int q_stride, const KVT* __
     const float* qrow = q + (size_t)row * q_stride + (size_t)h * (D + R);
     for (int i = threadIdx.x; i < D + R; i += blockDim.x) qraw[i] = qrow[i];
     __syncthreads();
-    for (int i = threadIdx.x; i < R / 2; i += blockDim.x) {
-        const float a = qraw[D + 2 * i], b = qraw[D + 2 * i + 1];
-        float ra = a, rb = b;
-        if (i < rot_pairs) {
-            float sn, cs;
-            sincosf((float)pos * freq[i], &sn, &cs);
-            ra = a * cs - b * sn;
-            rb = b * cs + a * sn;
-        }
-        qk[C + 2 * i] = ra * scale;
-        qk[C + 2 * i + 1] = rb * scale;
+    for (int i = threadIdx.x; i < rot_pairs; i += blockDim.x) {
+        const int ia = pair_first(i, rot_pairs, rot_halves), ib = pair_second(i, rot_pairs, rot_halves);
+        const float a = qraw[D + ia], b = qraw[D + ib];
+        float sn, cs;
+        sincosf((float)pos * freq[i], &sn, &cs);
+        sn *= rot_mag;
+        cs *= rot_mag;
+        qk[C + ia] = (a * cs - b * sn) * scale;
+        qk[C + ib] = (b * cs + a * sn) * scale;
     }
-    if ((R & 1) && threadIdx.x == 0) qk[C + R - 1] = qraw[D + R - 1] * scale;
+    for (int i = 2 * rot_pairs + threadIdx.x; i < R; i += blockDim.x) qk[C + i] = qraw[D + i] * scale;
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
         const WT* col = w_uk + (size_t)h * D * C + c;
         float s = 0.0f;
@@ -177,7 +180,8 @@ latent_attention_kernel(const float* __restrict__ q, int q_stride, const KVT* __
 
 template <typename WT, typename KVT>
 int launch_attention(int pl, dim3 grid, size_t smem, cudaStream_t stream, const float* q, int q_stride, const void* cache,
-                     const void* w_uk, const void* w_uv, void* out, const float* freq, int rot_pairs, const int* row_request,
+                     const void* w_uk, const void* w_uv, void* out, const float* freq, int rot_pairs, int rot_halves,
+                     float rot_mag, const int* row_request,
                      const int* positions, const int* block_tables, int table_stride, int heads, int D, int R, int V, int C,
                      int page_size, int window, float scale) {
 #define LLMX_LAT(P)                                                                                                       \
@@ -185,7 +189,7 @@ int launch_attention(int pl, dim3 grid, size_t smem, cudaStream_t stream, const 
         if (smem > 48 * 1024)                                                                                             \
             cudaFuncSetAttribute(latent_attention_kernel<WT, KVT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         launch_kernel(latent_attention_kernel<WT, KVT, P>, grid, dim3(WARPS * 32), smem, stream, q, q_stride,             \
-                      (const KVT*)cache, (const WT*)w_uk, (const WT*)w_uv, (WT*)out, freq, rot_pairs, row_request,        \
+                      (const KVT*)cache, (const WT*)w_uk, (const WT*)w_uv, (WT*)out, freq, rot_pairs, rot_halves, rot_mag, row_request, \
                       positions, block_tables, table_stride, heads, D, R, V, C, page_size, window, scale);               \
     } while (0)
     if (pl <= 2) LLMX_LAT(2);
@@ -214,8 +218,8 @@ int launch_attention(int pl, dim3 grid, size_t smem, cudaStream_t stream, const 
 template <typename WT, int ROWS_Q>
 __global__ void __launch_bounds__(128)
 latent_query_kernel(const float* __restrict__ q, int q_stride, const WT* __restrict__ w_uk, float* __restrict__ qk,
-                    const float* __restrict__ freq, int rot_pairs, const int* __restrict__ positions, int rows, int heads,
-                    int D, int R, int C, float scale) {
+                    const float* __restrict__ freq, int rot_pairs, int rot_halves, float rot_mag,
+                    const int* __restrict__ positions, int rows, int heads, int D, int R, int C, float scale) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float qraw[];            // ROWS_Q * (D + R)
@@ -228,22 +232,23 @@ latent_query_kernel(const float* __restrict__ q, int q_stride, const WT* __restr
     }
     __syncthreads();
     if (blockIdx.z == 0) {
-        for (int i = threadIdx.x; i < n * (R / 2); i += blockDim.x) {
-            const int r = i / (R / 2), k = i % (R / 2);
-            const float a = qraw[r * DR + D + 2 * k], b = qraw[r * DR + D + 2 * k + 1];
-            float ra = a, rb = b;
-            if (k < rot_pairs) {
-                float sn, cs;
-                sincosf((float)positions[r0 + r] * freq[k], &sn, &cs);
-                ra = a * cs - b * sn;
-                rb = b * cs + a * sn;
-            }
+        for (int i = threadIdx.x; i < n * rot_pairs; i += blockDim.x) {
+            const int r = i / rot_pairs, k = i % rot_pairs;
+            const int ia = pair_first(k, rot_pairs, rot_halves), ib = pair_second(k, rot_pairs, rot_halves);
+            const float a = qraw[r * DR + D + ia], b = qraw[r * DR + D + ib];
+            float sn, cs;
+            sincosf((float)positions[r0 + r] * freq[k], &sn, &cs);
+            sn *= rot_mag;
+            cs *= rot_mag;
             float* dst = qk + ((size_t)(r0 + r) * heads + h) * (C + R) + C;
-            dst[2 * k] = ra * scale;
-            dst[2 * k + 1] = rb * scale;
+            dst[ia] = (a * cs - b * sn) * scale;
+            dst[ib] = (b * cs + a * sn) * scale;
         }
-        if ((R & 1) && (int)threadIdx.x < n)
-            qk[((size_t)(r0 + threadIdx.x) * heads + h) * (C + R) + C + R - 1] = qraw[threadIdx.x * DR + DR - 1] * scale;
+        const int rest = R - 2 * rot_pairs;                       // values of the rotated part that no pair holds
+        for (int i = threadIdx.x; i < n * rest; i += blockDim.x) {
+            const int r = i / rest, k = 2 * rot_pairs + i % rest;
+            qk[((size_t)(r0 + r) * heads + h) * (C + R) + C + k] = qraw[r * DR + D + k] * scale;
+        }
     }
     const int c = blockIdx.z * blockDim.x + threadIdx.x;      // one column of the key map a thread
     if (c < C) {
@@ -831,8 +836,8 @@ LLMX_EXPORT void llmx_latent_tile_shape(int heads, int* heads_per_block, int* ro
 // The tiled form's three steps, each an entry point of its own (so that each shows in a profile).  Shapes as in
 // llmx_latent_attention.  qk: float [rows, heads, C + R]; part: float [rows, heads, splits, C + 2].
 LLMX_EXPORT int llmx_latent_query(const float* q, int q_stride, const void* w_uk, int w_dtype, float* qk, const float* freq,
-                                  int rot_pairs, const int* positions, int rows, int heads, int D, int R, int C, float scale,
-                                  cudaStream_t stream) {
+                                  int rot_pairs, int rot_halves, float rot_mag, const int* positions, int rows, int heads, int D,
+                                  int R, int C, float scale, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (heads <= 0 || heads > 65535 || D <= 0 || R < 0 || C <= 0 || 2 * rot_pairs > R) return LLMX_ERR_BAD_ARGUMENT;
     const int rq = rows > 64 ? 8 : 1;
@@ -841,7 +846,7 @@ LLMX_EXPORT int llmx_latent_query(const float* q, int q_stride, const void* w_uk
     const dim3 grid((rows + rq - 1) / rq, heads, (C + 127) / 128);
 #define LLMX_Q(WT, RQ)                                                                                                    \
     launch_kernel(latent_query_kernel<WT, RQ>, grid, dim3(128), smem, stream, q, q_stride, (const WT*)w_uk, qk, freq,      \
-                  rot_pairs, positions, rows, heads, D, R, C, scale)
+                  rot_pairs, rot_halves, rot_mag, positions, rows, heads, D, R, C, scale)
     if (w_dtype == LLMX_BF16) {
         if (rq == 8) LLMX_Q(__nv_bfloat16, 8);
         else LLMX_Q(__nv_bfloat16, 1);
@@ -916,13 +921,14 @@ LLMX_EXPORT int llmx_latent_merge(const float* part, const void* w_uv, int w_dty
 // cq [rows, Q] of `cq_dtype` (Q may be 0: no query latent in the rows); freq float [rot_pairs]; slots[row] = page *
 // page_size + offset (negative: no cache write for the row); cache [pages * page_size, C + R] of `cache_dtype`.
 LLMX_EXPORT int llmx_latent_write(const float* down, int stride, int Q, const float* wq, void* cq, int cq_dtype, const float* w,
-                                  float eps, const float* freq, int rot_pairs, const int* positions, const int* slots,
-                                  void* cache, int cache_dtype, int rows, int C, int R, cudaStream_t stream) {
+                                  float eps, const float* freq, int rot_pairs, int rot_halves, float rot_mag,
+                                  const int* positions, const int* slots, void* cache, int cache_dtype, int rows, int C, int R,
+                                  cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (C <= 0 || R < 0 || Q < 0 || 2 * rot_pairs > R || stride < Q + C + R) return LLMX_ERR_BAD_ARGUMENT;
 #define LLMX_LW(KVT, QT)                                                                                                  \
     launch_kernel(latent_write_kernel<KVT, QT>, dim3(rows), dim3(128), 0, stream, down, stride, Q, wq, (QT*)cq, w, eps,   \
-                  freq, rot_pairs, positions, slots, (KVT*)cache, C, R)
+                  freq, rot_pairs, rot_halves, rot_mag, positions, slots, (KVT*)cache, C, R)
     if (cache_dtype == LLMX_BF16 && cq_dtype == LLMX_BF16) LLMX_LW(__nv_bfloat16, __nv_bfloat16);
     else if (cache_dtype == LLMX_BF16 && cq_dtype == LLMX_F32) LLMX_LW(__nv_bfloat16, float);
     else if (cache_dtype == LLMX_F32 && cq_dtype == LLMX_BF16) LLMX_LW(float, __nv_bfloat16);
@@ -936,7 +942,7 @@ LLMX_EXPORT int llmx_latent_write(const float* down, int stride, int Q, const fl
 // of `w_dtype`, which is also the type of out [rows, heads * V].
 LLMX_EXPORT int llmx_latent_attention(const float* q, int q_stride, const void* cache, int cache_dtype, const void* w_uk,
                                       const void* w_uv, int w_dtype, void* out, const float* freq, int rot_pairs,
-                                      const int* row_request, const int* positions, const int* block_tables,
+                                      int rot_halves, float rot_mag, const int* row_request, const int* positions, const int* block_tables,
                                       int table_stride, int rows, int heads, int D, int R, int V, int C, int page_size,
                                       int window, float scale, cudaStream_t stream) {
     if (rows <= 0) return 0;
@@ -949,7 +955,7 @@ LLMX_EXPORT int llmx_latent_attention(const float* q, int q_stride, const void* 
     const dim3 grid(rows, heads);
 #define LLMX_GO(WT, KVT)                                                                                                  \
     return launch_attention<WT, KVT>(pl, grid, smem, stream, q, q_stride, cache, w_uk, w_uv, out, freq, rot_pairs,       \
-                                     row_request, positions, block_tables, table_stride, heads, D, R, V, C, page_size,   \
+                                     rot_halves, rot_mag, row_request, positions, block_tables, table_stride, heads, D, R, V, C, page_size,   \
                                      window, scale)
     if (w_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) LLMX_GO(__nv_bfloat16, __nv_bfloat16);
     if (w_dtype == LLMX_BF16 && cache_dtype == LLMX_F32) LLMX_GO(__nv_bfloat16, float);

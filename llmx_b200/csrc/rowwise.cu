@@ -448,7 +448,8 @@ constexpr int LN_MAX = 16;   // values a thread keeps (rows up to 16 * 256 wide)
 // `zero` (optional): a float buffer of `zero_count` values (a multiple of 4, 16-byte aligned) that the launch clears with
 // blocks of its own (those beyond `rows`): the outputs of products that follow and add their pieces with atomics.
 template <typename OutT>
-__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, OutT* __restrict__ y,
+__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ in_bias, const float* __restrict__ w,
+                                 const float* __restrict__ b, OutT* __restrict__ y, float* __restrict__ add_to, float mult,
                                  const int* __restrict__ row_index, int rows, int width, float eps,
                                  float* __restrict__ zero, long long zero_count) {
     pdl_trigger();
@@ -465,6 +466,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
     }
     const float* src = x + (size_t)(row_index ? row_index[r] : r) * width;
     OutT* dst = y + (size_t)r * width;
+    float* sum = add_to ? add_to + (size_t)r * width : nullptr;
     const float inv_n = 1.0f / (float)width;
     if (width <= LN_MAX * (int)blockDim.x) {
         float v[LN_MAX];
@@ -472,7 +474,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
 #pragma unroll
         for (int k = 0; k < LN_MAX; ++k) {
             const int i = threadIdx.x + k * blockDim.x;
-            v[k] = i < width ? src[i] : 0.0f;
+            v[k] = i < width ? src[i] + (in_bias ? in_bias[i] : 0.0f) : 0.0f;
             s += v[k];
         }
         const float mean = block_sum(s, scratch) * inv_n;
@@ -488,26 +490,38 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
 #pragma unroll
         for (int k = 0; k < LN_MAX; ++k) {
             const int i = threadIdx.x + k * blockDim.x;
-            if (i < width) dst[i] = from_float<OutT>(v[k] * rr * w[i]);
+            if (i < width) {
+                const float o = v[k] * rr * w[i] + (b ? b[i] : 0.0f);
+                if (sum) sum[i] = fmaf(mult, o, sum[i]);
+                else dst[i] = from_float<OutT>(o);
+            }
         }
         return;
     }
     float s = 0.0f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) s += src[i];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) s += src[i] + (in_bias ? in_bias[i] : 0.0f);
     const float mean = block_sum(s, scratch) * inv_n;
     float q = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float d = src[i] - mean;
+        const float d = src[i] + (in_bias ? in_bias[i] : 0.0f) - mean;
         q = fmaf(d, d, q);
     }
     const float rr = 1.0f / sqrtf(block_sum(q, scratch) * inv_n + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<OutT>((src[i] - mean) * rr * w[i]);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float o = (src[i] + (in_bias ? in_bias[i] : 0.0f) - mean) * rr * w[i] + (b ? b[i] : 0.0f);
+        if (sum) sum[i] = fmaf(mult, o, sum[i]);
+        else dst[i] = from_float<OutT>(o);
+    }
 }
 
-LLMX_EXPORT int llmx_layernorm(const float* x, const float* w, void* y, int out_dtype, const int* row_index, int rows,
-                               int width, float eps, float* zero, long long zero_count, cudaStream_t stream) {
+// The centred norm in its general form: y = ((x + in_bias) - mean) / sqrt(var + eps) * w + b.  `in_bias` and `b` may be
+// null.  With `add_to` (float [rows, width]) nothing is written to `y`; instead add_to += mult * y in 32-bit: the norm
+// after a sublayer and the sublayer's weighted entry into the residual stream in one pass.
+LLMX_EXPORT int llmx_layernorm_affine(const float* x, const float* in_bias, const float* w, const float* b, void* y, int out_dtype,
+                                      float* add_to, float mult, const int* row_index, int rows, int width, float eps,
+                                      float* zero, long long zero_count, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (width <= 0) return LLMX_ERR_BAD_ARGUMENT;
+    if (width <= 0 || (!y && !add_to)) return LLMX_ERR_BAD_ARGUMENT;
     if (zero && (zero_count % 4 || ((uintptr_t)zero & 15))) return LLMX_ERR_BAD_ARGUMENT;
     // The block width follows the row width alone, so a row's sums have one order whatever the batch.
     int threads = (width + LN_MAX - 1) / LN_MAX;
@@ -517,10 +531,59 @@ LLMX_EXPORT int llmx_layernorm(const float* x, const float* w, void* y, int out_
     long long zero_blocks = zero ? (zero_count / 4 + 4 * threads - 1) / (4 * threads) : 0;
     zero_blocks = zero_blocks > 1024 ? 1024 : zero_blocks;
     const dim3 grid((unsigned)(rows + zero_blocks));
-    if (out_dtype == LLMX_BF16)
-        launch_kernel(layernorm_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, x, w, (__nv_bfloat16*)y, row_index, rows, width, eps, zero, zero_count);
+    if (out_dtype == LLMX_BF16 && !add_to)
+        launch_kernel(layernorm_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, x, in_bias, w, b, (__nv_bfloat16*)y, add_to, mult,
+                      row_index, rows, width, eps, zero, zero_count);
     else
-        launch_kernel(layernorm_kernel<float>, grid, dim3(threads), 0, stream, x, w, (float*)y, row_index, rows, width, eps, zero, zero_count);
+        launch_kernel(layernorm_kernel<float>, grid, dim3(threads), 0, stream, x, in_bias, w, b, (float*)y, add_to, mult, row_index, rows,
+                      width, eps, zero, zero_count);
+    return launch_status();
+}
+
+LLMX_EXPORT int llmx_layernorm(const float* x, const float* w, void* y, int out_dtype, const int* row_index, int rows,
+                               int width, float eps, float* zero, long long zero_count, cudaStream_t stream) {
+    return llmx_layernorm_affine(x, nullptr, w, nullptr, y, out_dtype, nullptr, 0.0f, row_index, rows, width, eps, zero, zero_count,
+                                 stream);
+}
+
+// ---------------------------------------------------------------------------
+// A gate on rows: o[r, c] *= sigmoid(gate[r, c]) in 32-bit, o of the path's type in place; `gate` is float and has a
+// row stride of its own (it lies inside a wider product's output).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ o, const float* __restrict__ gate, int gate_stride, int width, long long total) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float g = gate[(i / width) * gate_stride + (i % width)];
+    o[i] = from_float<T>(to_float(o[i]) / (1.0f + expf(-g)));
+}
+
+LLMX_EXPORT int llmx_sigmoid_gate(void* o, int dtype, const float* gate, int gate_stride, int rows, int width, cudaStream_t stream) {
+    const long long total = (long long)rows * width;
+    if (total <= 0) return 0;
+    if (gate_stride < width) return LLMX_ERR_BAD_ARGUMENT;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == LLMX_BF16) launch_kernel(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)o, gate, gate_stride, width, total);
+    else launch_kernel(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)o, gate, gate_stride, width, total);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// x[r, c] += bias[c]: the bias of a product whose result was added into x.
+// ---------------------------------------------------------------------------
+__global__ void add_bias_kernel(float* __restrict__ x, const float* __restrict__ bias, int width, long long total) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] += bias[i % width];
+}
+
+LLMX_EXPORT int llmx_add_bias(float* x, const float* bias, int rows, int width, cudaStream_t stream) {
+    const long long total = (long long)rows * width;
+    if (total <= 0) return 0;
+    launch_kernel(add_bias_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, bias, width, total);
     return launch_status();
 }
 

@@ -36,7 +36,8 @@ class LayerStep:
     block: int                          # index into Model.blocks
     cache_entry: Optional[Union[int, Tuple[int, ...]]] = None   # index of the cache entry the mixer uses (None: the mixer has
     #                                     no cache; a tuple: one entry for each spec of a mixer that needs several)
-    write_cache: bool = True            # False: read the entry another step wrote
+    write_cache: Union[bool, Tuple[bool, ...]] = True   # False: read the entry another step wrote; a tuple: one flag for
+    #                                     each of several entries (a mixer that reads another layer's keys beside state of its own)
     add_embedding: bool = False         # the embedding output is added to the stream before the block runs
 
 
@@ -121,9 +122,12 @@ class Model:
             if len(entries) != len(specs):
                 need = "a cache entry" if len(specs) == 1 else f"{len(specs)} cache entries"
                 raise ValueError(f"layer order step {n}: block {s.block} needs {need}" + (f", {len(entries)} named" if entries else ""))
-            for e in entries:
+            writes = tuple(s.write_cache) if isinstance(s.write_cache, (tuple, list)) else (s.write_cache,) * len(entries)
+            if len(writes) != len(entries):
+                raise ValueError(f"layer order step {n}: {len(entries)} cache entries but {len(writes)} write flags")
+            for e, writing in zip(entries, writes):
                 named.add(e)
-                if s.write_cache:
+                if writing:
                     if e in writers:
                         raise ValueError(f"layer order steps {writers[e]} and {n} both write cache entry {e}")
                     writers[e] = n
@@ -204,7 +208,8 @@ class Model:
             self._native_tried = True
             blocks = [b.native for b in self.blocks]
             emb, head = self.embedding.native, self.head.native
-            plain = all(not s.add_embedding and not isinstance(s.cache_entry, (tuple, list)) for s in self.order)
+            plain = all(not s.add_embedding and not isinstance(s.cache_entry, (tuple, list)) and isinstance(s.write_cache, bool)
+                        for s in self.order)
             if emb and head and all(blocks) and plain:
                 arr = (ctypes.c_void_p * len(blocks))(*blocks)
                 order = (runtime.LayerStepStruct * len(self.order))(*[

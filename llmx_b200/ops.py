@@ -97,6 +97,9 @@ _SIGNATURES = {
     ("rowwise", "llmx_embed_scaled"): [_p, _i, _p, _p, _i, _i, _i, _f, _p],
     ("rowwise", "llmx_scale"): [_p, ctypes.c_longlong, _f, _p],
     ("rowwise", "llmx_layernorm"): [_p, _p, _p, _i, _p, _i, _i, _f, _p, ctypes.c_longlong, _p],
+    ("rowwise", "llmx_layernorm_affine"): [_p, _p, _p, _p, _p, _i, _p, _f, _p, _i, _i, _f, _p, ctypes.c_longlong, _p],
+    ("rowwise", "llmx_sigmoid_gate"): [_p, _i, _p, _i, _i, _i, _p],
+    ("rowwise", "llmx_add_bias"): [_p, _p, _i, _i, _p],
     ("rowwise", "llmx_clamped_glu"): [_p, _p, _i, _i, _i, _f, _f, _p],
     ("rowwise", "llmx_silu_columns"): [_p, _i, _i, _i, _i, _p],
     ("rowwise", "llmx_gated_rmsnorm"): [_p, _p, _i, _p, _i, _p, _i, _i, _i, _i, _f, _i, _i, _p],
@@ -107,6 +110,8 @@ _SIGNATURES = {
     ("recurrence", "llmx_conv_prepare"): [_p, _i, _i, _i, _i, _i, _p, _p, _i, _p, _p, _p, _i, _i, _i, _p, _i, _p, _i, _i, _i, _f,
                                           _p, ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _i, _i, _p],
     ("attention_split", "llmx_qk_norm_rope_write"): [_p, _i, _p, _p, _f, _p, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p],
+    ("attention_split", "llmx_qkv_finish"): [_p, _i, _p, _p, _i, _p, ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _p, _p, _i,
+                                             _f, _p, _i, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p],
     ("attention_split", "llmx_attention_split"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
     ("attention_split", "llmx_attention_tiled_fits"): [_i, _i, _i, _i],
     ("attention_split", "llmx_attention_tiled"): [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
@@ -114,10 +119,10 @@ _SIGNATURES = {
     ("moe", "llmx_moe_product_few"): [_p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _i, _i, _i, _i, _p],
     ("moe", "llmx_moe_product"): [_p, _i, _p, _i, _p, _p, _p, _i, _i, _p, _i, _i, _i, _i, _i, _p],
     ("moe", "llmx_moe_combine"): [_p, _p, _i, _i, _i, _f, _p],
-    ("latent_attention", "llmx_latent_write"): [_p, _i, _i, _p, _p, _i, _p, _f, _p, _i, _p, _p, _p, _i, _i, _i, _i, _p],
-    ("latent_attention", "llmx_latent_attention"): [_p, _i, _p, _i, _p, _p, _i, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i,
+    ("latent_attention", "llmx_latent_write"): [_p, _i, _i, _p, _p, _i, _p, _f, _p, _i, _i, _f, _p, _p, _p, _i, _i, _i, _i, _p],
+    ("latent_attention", "llmx_latent_attention"): [_p, _i, _p, _i, _p, _p, _i, _p, _p, _i, _i, _f, _p, _p, _p, _i, _i, _i, _i,
                                                     _i, _i, _i, _i, _i, _f, _p],
-    ("latent_attention", "llmx_latent_query"): [_p, _i, _p, _i, _p, _p, _i, _p, _i, _i, _i, _i, _i, _f, _p],
+    ("latent_attention", "llmx_latent_query"): [_p, _i, _p, _i, _p, _p, _i, _i, _f, _p, _i, _i, _i, _i, _i, _f, _p],
     ("latent_attention", "llmx_latent_scores"): [_p, _p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
     ("latent_attention", "llmx_latent_merge"): [_p, _p, _i, _p, _i, _i, _i, _i, _i, _p],
     ("gemm_plain", "llmx_gemm_plain"): [_p, _i, _p, _i, _p, _i, _i, _i, _i, _p],
@@ -333,22 +338,63 @@ def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
 
 
 def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-              row_index: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[i] = (x - mean) / sqrt(var + eps) * weight over row (row_index[i] or i); x float32, out float32 or bfloat16.
+              row_index: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None,
+              bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = (x - mean) / sqrt(var + eps) * weight (+ bias) over row (row_index[i] or i); x float32, out float32 or bfloat16.
     `zero` (optional): a float32 tensor the same launch clears (outputs of products that follow and add their pieces)."""
-    _cuda(x, weight, out, row_index, zero)
+    _cuda(x, weight, out, row_index, zero, bias)
     if zero is not None:
         _need(zero.dtype == torch.float32 and zero.numel() % 4 == 0, "layernorm: the buffer to clear must be float32, a multiple of 4 long")
     rows, width = out.shape
     _need(x.dtype == torch.float32 and weight.dtype == torch.float32, "layernorm: input and weight must be float32")
     _need(x.dim() == 2 and x.shape[1] == width and weight.numel() == width, "layernorm: widths do not fit")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == width), "layernorm: bias float32 of the row's width")
     if row_index is None:
         _need(x.shape[0] >= rows, "layernorm: fewer input rows than output rows")
     else:
         _need(row_index.dtype == torch.int32 and row_index.numel() == rows, "layernorm: row_index must be int32 per row")
-    _check(_fn("rowwise", "llmx_layernorm")(_ptr(x), _ptr(weight), _ptr(out), _code(out), _ptr(row_index), rows, width,
-                                            float(eps), _ptr(zero), 0 if zero is None else zero.numel(), _stream()), "layernorm")
+    _check(_fn("rowwise", "llmx_layernorm_affine")(_ptr(x), None, _ptr(weight), _ptr(bias), _ptr(out), _code(out), None, 0.0,
+                                                   _ptr(row_index), rows, width, float(eps), _ptr(zero),
+                                                   0 if zero is None else zero.numel(), _stream()), "layernorm")
     return out
+
+
+def layernorm_add_(residual: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float,
+                   factor: float, in_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual += factor * ((z - mean) / sqrt(var + eps) * weight + bias), z = y + in_bias, row by row; all float32.
+    The norm after a sublayer and the sublayer's weighted entry into the stream in one kernel; `in_bias`: a bias the
+    sublayer's last product left for whoever reads its output."""
+    _cuda(residual, y, weight, bias, in_bias)
+    rows, width = residual.shape
+    _need(residual.dtype == torch.float32 and y.dtype == torch.float32 and tuple(y.shape) == (rows, width),
+          "layernorm_add: float32 tensors of one shape")
+    for t in (weight, bias, in_bias):
+        _need(t is None or (t.dtype == torch.float32 and t.numel() == width), "layernorm_add: float32 vectors of the row's width")
+    _need(weight is not None, "layernorm_add: a weight")
+    _check(_fn("rowwise", "llmx_layernorm_affine")(_ptr(y), _ptr(in_bias), _ptr(weight), _ptr(bias), None, F32, _ptr(residual),
+                                                   float(factor), None, rows, width, float(eps), None, 0, _stream()), "layernorm_add")
+    return residual
+
+
+def add_bias_(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """x[r, :] += bias; float32."""
+    _cuda(x, bias)
+    _need(x.dtype == torch.float32 and bias.dtype == torch.float32 and x.dim() == 2 and bias.numel() == x.shape[1],
+          "add_bias: float32 rows and a bias of their width")
+    _check(_fn("rowwise", "llmx_add_bias")(_ptr(x), _ptr(bias), x.shape[0], x.shape[1], _stream()), "add_bias")
+    return x
+
+
+def sigmoid_gate_(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """o *= sigmoid(gate) in place; o [rows, width] of the path's type, contiguous; gate float32 [rows, width], a view whose
+    rows may be strided."""
+    _need(o.is_cuda and gate.is_cuda, "kernel arguments must be CUDA tensors (there is no CPU path)")
+    rows, width = o.shape
+    _need(o.is_contiguous() and gate.dtype == torch.float32 and tuple(gate.shape) == (rows, width) and gate.stride(1) == 1,
+          "sigmoid_gate: contiguous rows and a float32 gate of the same shape")
+    _check(_fn("rowwise", "llmx_sigmoid_gate")(_ptr(o), _code(o), _ptr(gate), gate.stride(0) if rows > 1 else width, rows, width,
+                                               _stream()), "sigmoid_gate")
+    return o
 
 
 def clamped_glu(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
@@ -526,6 +572,48 @@ def qk_norm_rope_write(proj: torch.Tensor, heads: int, kv_heads: int, key_dim: i
         _stream()), "qk_norm_rope_write")
 
 
+def qkv_finish(proj: torch.Tensor, heads: int, kv_heads: int, key_dim: int, value_dim: int, step, q_out: torch.Tensor,
+               cache: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+               taps_w: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None, conv_off: int = 0,
+               norm: str = "none", q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+               freq: Optional[torch.Tensor] = None, neighbours: bool = False) -> None:
+    """The general finishing of a stacked q/k/v product's rows (csrc/attention_split.cu, `QkvFinish`): proj float32 [rows, q
+    (heads * D) | k (kv_heads * D) | v (kv_heads * V)] (a view whose rows may be strided; kv_heads 0: queries alone) plus
+    `bias` [channels]; a causal filter `taps_w` [channels, taps] per channel whose earlier inputs lie in `state`
+    [slots, floats] at `conv_off` ([taps - 1][channels], read at the request's slot, written at its spare); an RMS norm
+    per q and k head `norm` = "none" | "before" | "after" the rotation, with weights [D] or without; a rotation of the
+    first 2 * len(freq) values of a head by position * freq[i], pairs (i, i + len(freq)) or `neighbours` (2i, 2i + 1);
+    queries to q_out [rows, heads * D], [k ; v] to cache [pages, 1, kv_heads, page, D + V] at `slots`.  `step`: the StepBatch."""
+    _cuda(bias, taps_w, state, q_weight, k_weight, freq, slots, q_out, cache)
+    rows = proj.shape[0]
+    channels = (heads + kv_heads) * key_dim + kv_heads * value_dim
+    _need(proj.is_cuda and proj.dtype == torch.float32 and proj.dim() == 2 and proj.shape[1] == channels and proj.stride(1) == 1,
+          "qkv_finish: product rows float32 [rows, q | k | v]")
+    _need(tuple(q_out.shape) == (rows, heads * key_dim) and rows == step.rows, "qkv_finish: q_out shape or the step's rows do not fit")
+    _need(norm in ("none", "before", "after"), "qkv_finish: norm is none, before or after")
+    for t, n in ((bias, channels), (q_weight, key_dim), (k_weight, key_dim)):
+        _need(t is None or (t.dtype == torch.float32 and t.numel() == n), "qkv_finish: float32 bias [channels], norm weights [D]")
+    taps = 1
+    if taps_w is not None:
+        taps = taps_w.shape[1]
+        _need(taps_w.dtype == torch.float32 and tuple(taps_w.shape) == (channels, taps), "qkv_finish: taps float32 [channels, taps]")
+    if taps > 1:
+        _need(state is not None and state.dtype == torch.float32 and state.dim() == 2
+              and conv_off + (taps - 1) * channels <= state.shape[1], "qkv_finish: state slots too small for the filter's inputs")
+    if kv_heads:
+        _need(cache is not None and slots is not None and cache.dim() == 5 and cache.shape[1] == 1 and cache.shape[2] == kv_heads
+              and cache.shape[4] == key_dim + value_dim and slots.dtype == torch.int32 and slots.numel() >= rows,
+              "qkv_finish: cache layout or slots do not fit")
+    _need(freq is None or (freq.dtype == torch.float32 and 2 * freq.numel() <= key_dim), "qkv_finish: frequencies float32 [<= D / 2]")
+    _check(_fn("attention_split", "llmx_qkv_finish")(
+        _ptr(proj), proj.stride(0) if rows > 1 else proj.shape[1], _ptr(bias), _ptr(taps_w), taps, _ptr(state),
+        0 if state is None else state.shape[1], int(conv_off), _ptr(step.row_request), _ptr(step.row_start), _ptr(step.row_count),
+        _ptr(step.history), _ptr(step.state_slots), _ptr(step.state_slots_out), _ptr(q_weight), _ptr(k_weight),
+        ("none", "before", "after").index(norm), float(eps), _ptr(freq), 0 if freq is None else freq.numel(), 1 if neighbours else 0,
+        _ptr(step.positions), _ptr(slots), _ptr(q_out), _code(q_out), _ptr(cache), _code(cache) if cache is not None else F32, rows,
+        step.requests, heads, kv_heads, key_dim, value_dim, cache.shape[3] if cache is not None else 1, _stream()), "qkv_finish")
+
+
 def attention_split(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row_request: torch.Tensor,
                     positions: torch.Tensor, block_tables: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
                     value_dim: int, window: Optional[int], chunk: Optional[int], scale: float, splits: int = 1) -> torch.Tensor:
@@ -657,13 +745,15 @@ def moe_combine_(x: torch.Tensor, y: torch.Tensor, top: int, weight: float) -> t
 # Attention over a cache of latents.
 def latent_write(down: torch.Tensor, q_rank: int, q_weight: Optional[torch.Tensor], cq: Optional[torch.Tensor], weight: torch.Tensor,
                  eps: float, freq: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, cache: torch.Tensor, latent: int,
-                 rot: int) -> None:
+                 rot: int, halves: bool = False, magnitude: float = 1.0) -> None:
     """Rows of the stacked down projections [query latent | key/value latent | rotated key part]:
     cq = rmsnorm(query latent) * q_weight (in cq's type; `q_rank` 0: the rows hold no query latent), and
-    cache[slot] = [rmsnorm(key/value latent) * weight ; rotate(rotated part)]; cache [pages, 1, 1, page, latent + rot]."""
-    _cuda(down, q_weight, cq, weight, freq, positions, slots, cache)
+    cache[slot] = [rmsnorm(key/value latent) * weight ; rotate(rotated part)]; cache [pages, 1, 1, page, latent + rot].
+    `down` may be a view of the first columns of a wider product's output.  `halves`: rotation pair i is (i, i + pairs)
+    instead of neighbours; `magnitude`: a factor on cosines and sines."""
+    _need(all(t is None or t.is_cuda for t in (down, q_weight, cq, weight, freq, positions, slots, cache)), "kernel arguments must be CUDA tensors (there is no CPU path)")
     rows = down.shape[0]
-    _need(down.dtype == torch.float32 and down.dim() == 2 and down.shape[1] == q_rank + latent + rot,
+    _need(down.dtype == torch.float32 and down.dim() == 2 and down.shape[1] == q_rank + latent + rot and down.stride(1) == 1,
           "latent_write: down projections float32 [rows, q_rank + latent + rot]")
     if q_rank:
         _need(q_weight is not None and cq is not None and q_weight.dtype == torch.float32 and q_weight.numel() == q_rank
@@ -673,31 +763,32 @@ def latent_write(down: torch.Tensor, q_rank: int, q_weight: Optional[torch.Tenso
     _need(cache.shape[-1] == latent + rot, "latent_write: cache rows do not fit")
     _need(positions.dtype == torch.int32 and slots.dtype == torch.int32 and positions.numel() >= rows and slots.numel() >= rows,
           "latent_write: positions and slots must be int32 per row")
-    _check(_fn("latent_attention", "llmx_latent_write")(_ptr(down), down.shape[1], int(q_rank), _ptr(q_weight), _ptr(cq),
+    _check(_fn("latent_attention", "llmx_latent_write")(_ptr(down), down.stride(0) if rows > 1 else down.shape[1], int(q_rank), _ptr(q_weight), _ptr(cq),
                                                         _code(cq) if cq is not None else F32, _ptr(weight), float(eps), _ptr(freq),
-                                                        freq.numel(), _ptr(positions), _ptr(slots), _ptr(cache), _code(cache), rows,
-                                                        latent, rot, _stream()), "latent_write")
+                                                        freq.numel(), 1 if halves else 0, float(magnitude), _ptr(positions), _ptr(slots),
+                                                        _ptr(cache), _code(cache), rows, latent, rot, _stream()), "latent_write")
 
 
 def latent_attention(q: torch.Tensor, cache: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor, out: torch.Tensor,
                      freq: torch.Tensor, row_request: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor,
                      heads: int, key_dim: int, rot: int, value_dim: int, latent: int, page_size: int,
-                     window: Optional[int], scale: float) -> torch.Tensor:
+                     window: Optional[int], scale: float, halves: bool = False, magnitude: float = 1.0) -> torch.Tensor:
     """Softmax attention of query heads [key_dim unrotated ; rot rotated] over cached [latent ; rotated key part] rows, the
     keys and values of a head being linear maps of the latent (csrc/latent_attention.cu).  q float32 [rows, heads *
     (key_dim + rot)]; w_uk [heads * key_dim, latent], w_uv [heads * value_dim, latent] and out [rows, heads * value_dim]
-    of one type."""
-    _cuda(q, cache, w_uk, w_uv, out, freq, row_request, positions, block_tables)
+    of one type.  q may be a view of columns of a wider product's output."""
+    _cuda(cache, w_uk, w_uv, out, freq, row_request, positions, block_tables)
     rows = q.shape[0]
-    _need(q.dtype == torch.float32 and q.shape[1] == heads * (key_dim + rot), "latent_attention: queries float32 [rows, heads * (key_dim + rot)]")
+    _need(q.is_cuda and q.dtype == torch.float32 and q.shape[1] == heads * (key_dim + rot) and q.stride(1) == 1,
+          "latent_attention: queries float32 [rows, heads * (key_dim + rot)]")
     _need(tuple(w_uk.shape) == (heads * key_dim, latent) and tuple(w_uv.shape) == (heads * value_dim, latent)
           and w_uk.dtype == w_uv.dtype == out.dtype, "latent_attention: key and value maps do not fit")
     _need(tuple(out.shape) == (rows, heads * value_dim) and cache.shape[-1] == latent + rot, "latent_attention: output or cache rows do not fit")
     for t in (row_request, positions, block_tables):
         _need(t.dtype == torch.int32, "latent_attention: metadata must be int32")
     _check(_fn("latent_attention", "llmx_latent_attention")(
-        _ptr(q), q.shape[1], _ptr(cache), _code(cache), _ptr(w_uk), _ptr(w_uv), _code(w_uk), _ptr(out), _ptr(freq), freq.numel(),
-        _ptr(row_request), _ptr(positions), _ptr(block_tables), block_tables.shape[1], rows, heads, key_dim, rot, value_dim,
+        _ptr(q), q.stride(0) if rows > 1 else q.shape[1], _ptr(cache), _code(cache), _ptr(w_uk), _ptr(w_uv), _code(w_uk), _ptr(out),
+        _ptr(freq), freq.numel(), 1 if halves else 0, float(magnitude), _ptr(row_request), _ptr(positions), _ptr(block_tables), block_tables.shape[1], rows, heads, key_dim, rot, value_dim,
         latent, page_size, int(window or 0), float(scale), _stream()), "latent_attention")
     return out
 
@@ -713,15 +804,17 @@ def latent_tile_shape(heads: int):
 def latent_attention_tiled(q: torch.Tensor, cache: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor, out: torch.Tensor,
                            freq: torch.Tensor, row_request: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor,
                            tiles: torch.Tensor, n_tiles: int, splits: int, heads: int, key_dim: int, rot: int, value_dim: int,
-                           latent: int, page_size: int, window: Optional[int], scale: float, plain_cores: bool = False) -> torch.Tensor:
+                           latent: int, page_size: int, window: Optional[int], scale: float, plain_cores: bool = False,
+                           halves: bool = False, magnitude: float = 1.0) -> torch.Tensor:
     """`latent_attention` in its tiled form (csrc/latent_attention.cu): `tiles` int32 [n_tiles, 2] on the device, the
     first row and the row count of every tile (rows of one request, at most `latent_tile_shape`'s); `splits` ranges
     of a tile's keys run as blocks of their own and are merged.  With a bfloat16 cache and a latent of 128, 256 or 512
     values the scores run on the tensor cores, 32-bit factors as sums of three bfloat16 values; `plain_cores` keeps
     them on the CUDA cores."""
-    _cuda(q, cache, w_uk, w_uv, out, freq, row_request, positions, block_tables, tiles)
+    _cuda(cache, w_uk, w_uv, out, freq, row_request, positions, block_tables, tiles)
     rows = q.shape[0]
-    _need(q.dtype == torch.float32 and q.shape[1] == heads * (key_dim + rot), "latent_attention: queries float32 [rows, heads * (key_dim + rot)]")
+    _need(q.is_cuda and q.dtype == torch.float32 and q.shape[1] == heads * (key_dim + rot) and q.stride(1) == 1,
+          "latent_attention: queries float32 [rows, heads * (key_dim + rot)]")
     _need(tuple(w_uk.shape) == (heads * key_dim, latent) and tuple(w_uv.shape) == (heads * value_dim, latent)
           and w_uk.dtype == w_uv.dtype == out.dtype, "latent_attention: key and value maps do not fit")
     _need(tuple(out.shape) == (rows, heads * value_dim) and cache.shape[-1] == latent + rot, "latent_attention: output or cache rows do not fit")
@@ -730,7 +823,8 @@ def latent_attention_tiled(q: torch.Tensor, cache: torch.Tensor, w_uk: torch.Ten
     _need(tiles.numel() >= 2 * n_tiles and n_tiles > 0 and splits > 0, "latent_attention: tiles do not fit")
     qk = torch.empty((rows, heads, latent + rot), dtype=torch.float32, device=q.device)
     part = torch.empty((rows, heads, splits, latent + 2), dtype=torch.float32, device=q.device)
-    _check(_fn("latent_attention", "llmx_latent_query")(_ptr(q), q.shape[1], _ptr(w_uk), _code(w_uk), _ptr(qk), _ptr(freq), freq.numel(),
+    _check(_fn("latent_attention", "llmx_latent_query")(_ptr(q), q.stride(0) if rows > 1 else q.shape[1], _ptr(w_uk), _code(w_uk), _ptr(qk),
+                                                        _ptr(freq), freq.numel(), 1 if halves else 0, float(magnitude),
                                                         _ptr(positions), rows, heads, key_dim, rot, latent, float(scale), _stream()),
            "latent_query")
     _check(_fn("latent_attention", "llmx_latent_scores")(_ptr(qk), _ptr(cache), _code(cache), _ptr(part), _ptr(tiles), int(n_tiles),

@@ -5,7 +5,7 @@ from .norm import LayerNorm, RMSNorm
 from .rope import NoPositionEncoding, RotaryEmbedding
 from .attention import Attention
 from .mlp import ClampedGLU, GatedMLP, TableRoutedExperts
-from .block import ParallelBlock, PreNormBlock
+from .block import ParallelBlock, PreNormBlock, SandwichBlock
 from .linear_attention import DecayedLinearAttention
 from .delta_rule import GatedDeltaRule
 from .latent_attention import LatentAttention
@@ -17,4 +17,4 @@ from .mixer_pair import MixerPair
 __all__ = ["GroupView", "Part", "Precision", "StepBatch", "Linear", "RMSNorm", "NoPositionEncoding",
            "RotaryEmbedding", "Attention", "GatedMLP", "PreNormBlock", "LogitsHead", "TokenEmbedding", "LayerNorm", "ClampedGLU",
            "ParallelBlock", "DecayedLinearAttention", "GatedDeltaRule", "LatentAttention",
-           "TableRoutedExperts", "SelectiveStateSpace", "MaskedAttention", "MixerPair"]
+           "TableRoutedExperts", "SelectiveStateSpace", "MaskedAttention", "MixerPair", "SandwichBlock"]

@@ -1,4 +1,6 @@
 """How a layer's parts are arranged.  PreNormBlock: x += mixer(norm(x)); x += ffn(norm(x)).
+ParallelBlock: x += mixer(norm(x)) + ffn(norm(x)).  SandwichBlock: a norm before and after each sublayer and a factor
+on what enters the stream: x += m * norm_b(mixer(norm_a(x))); x += m * norm_d(ffn(norm_c(x))).
 
 The names of the four parts (the prefixes of their tensors) are arguments, so
 the arrangement knows no architecture's tensor names.  When all four parts have a twin in the native runtime
@@ -117,3 +119,48 @@ class ParallelBlock(Part):
         self.mixer.forward(h, step, cache_entry, x, write_cache)
         if self.ffn is not None:
             self.ffn.forward(h, step, x)
+
+
+class SandwichBlock(Part):
+    """x += factor * post_mixer_norm(mixer(pre_mixer_norm(x))); then, with a feed-forward,
+    x += factor * post_ffn_norm(ffn(pre_ffn_norm(x))).  A sublayer's output is gathered in a float32 buffer of its own
+    (cleared by the launch of the norm before the sublayer), and the norm after it adds into the stream in the same
+    kernel that norms (`add_into(residual, y, factor, in_bias)` of the norm part).  A mixer that says so
+    (`defer_output_bias`) leaves the bias of its output projection to that kernel.  `ffn` and its two norms may be None.
+    `names`: the prefixes of the six parts' tensors."""
+
+    def __init__(self, pre_mixer_norm: Part, mixer: Part, post_mixer_norm: Part, pre_ffn_norm: Optional[Part], ffn: Optional[Part],
+                 post_ffn_norm: Optional[Part], factor: float = 1.0,
+                 names=("norm1", "mix", "norm1b", "norm2", "mlp", "norm2b")):
+        if (ffn is None) != (pre_ffn_norm is None) or (ffn is None) != (post_ffn_norm is None):
+            raise ValueError("sandwich block: a feed-forward comes with both of its norms, or none of the three")
+        self.pre_mixer_norm, self.mixer, self.post_mixer_norm = pre_mixer_norm, mixer, post_mixer_norm
+        self.pre_ffn_norm, self.ffn, self.post_ffn_norm = pre_ffn_norm, ffn, post_ffn_norm
+        self.factor, self.names = float(factor), tuple(names)
+        if hasattr(mixer, "defer_output_bias"):
+            mixer.defer_output_bias = True
+
+    def children(self) -> Dict[str, Part]:
+        parts = (self.pre_mixer_norm, self.mixer, self.post_mixer_norm, self.pre_ffn_norm, self.ffn, self.post_ffn_norm)
+        return {n: p for n, p in zip(self.names, parts) if p is not None}
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, x: torch.Tensor, step: StepBatch, cache_entry, write_cache=True) -> None:
+        """x: the float32 residual stream [rows, hidden], updated in place."""
+        rows, width = x.shape
+        both = self.ffn is not None
+        n = rows * width
+        pad = (n + 3) & ~3                                  # the second buffer starts on a 16-byte boundary
+        flat = torch.empty(pad * (2 if both else 1), dtype=torch.float32, device=x.device)
+        out = flat[:n].view(rows, width)
+        h = self.pre_mixer_norm.forward(x, zero=flat[:pad])
+        self.mixer.forward(h, step, cache_entry, out, write_cache)
+        pending = getattr(self.mixer, "output_bias", None) if getattr(self.mixer, "defer_output_bias", False) else None
+        self.post_mixer_norm.add_into(x, out, self.factor, in_bias=pending)
+        if both:
+            out = flat[pad:pad + n].view(rows, width)
+            h = self.pre_ffn_norm.forward(x, zero=flat[pad:])
+            self.ffn.forward(h, step, out)
+            self.post_ffn_norm.add_into(x, out, self.factor)

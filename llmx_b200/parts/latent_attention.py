@@ -11,6 +11,14 @@ Only [c | r] is cached, one vector per token (a cache entry of one plane).  The 
 (2i, 2i + 1) of the first `rot_dims` values of the rotated part by the angle p * base^(-2i / rot_dims).  The kernels
 (csrc/latent_attention.cu) never make keys or values of cached tokens: the query goes through Wuk once, the weighted
 sum of latents through Wuv once.
+
+Options for designs that vary it:
+    q_rank None        no query latent: q = h Wq^T straight from the input (tensor role `q` instead of dq, dq.norm, uq)
+    pairing "halves"   rotation pair i is (i, i + rot_dims / 2) instead of neighbours
+    rot_scaling        (factor, original, fast, slow): frequencies blended for contexts longer than the original one and
+                       a factor on cosines and sines (`parts.rope.blended_frequencies`); the score scale stays as given
+    gate True          the concatenated heads are multiplied by sigmoid(h Wg^T) before the output product (role `g`)
+Whatever reads h is one product over the stacked weight.
 """
 from __future__ import annotations
 
@@ -24,6 +32,7 @@ from ..cache.manager import KVSpec
 from ..weights.spec import TensorSpec
 from .base import Part, PartPlan, Precision, StepBatch, StepShape
 from .linear import Linear, stored_product
+from .rope import blended_frequencies, power_frequencies
 
 
 class _TilePlan(PartPlan):
@@ -39,12 +48,18 @@ class _TilePlan(PartPlan):
 
 
 class LatentAttention(Part):
-    def __init__(self, hidden: int, heads: int, key_dim: int, rot_dim: int, value_dim: int, q_rank: int, kv_rank: int,
-                 scale: float, rot_base: float, rot_dims: int, norm_eps: float, window: Optional[int] = None):
+    def __init__(self, hidden: int, heads: int, key_dim: int, rot_dim: int, value_dim: int, q_rank: Optional[int], kv_rank: int,
+                 scale: float, rot_base: float, rot_dims: int, norm_eps: float, window: Optional[int] = None,
+                 pairing: str = "neighbours", rot_scaling=None, gate: bool = False):
         if rot_dims % 2 or rot_dims > rot_dim or rot_dims < 0:
             raise ValueError("latent attention: the rotated width must be even and at most the rotated part's width")
+        if pairing not in ("neighbours", "halves"):
+            raise ValueError("latent attention: rotation pairs are neighbours or halves")
         self.hidden, self.heads, self.key_dim, self.rot_dim, self.value_dim = int(hidden), int(heads), int(key_dim), int(rot_dim), int(value_dim)
-        self.q_rank, self.kv_rank, self.scale = int(q_rank), int(kv_rank), float(scale)
+        self.q_rank, self.kv_rank, self.scale = int(q_rank or 0), int(kv_rank), float(scale)
+        self.pairing, self.gate = pairing, bool(gate)
+        self.rot_scaling = tuple(float(x) for x in rot_scaling) if rot_scaling is not None else None
+        self.rot_magnitude = 1.0
         self.rot_base, self.rot_dims, self.norm_eps = float(rot_base), int(rot_dims), float(norm_eps)
         self.window = int(window) if window else None
         self.q_width = self.heads * (self.key_dim + self.rot_dim)
@@ -54,32 +69,51 @@ class LatentAttention(Part):
 
     def stored_products(self):
         """The products whose result is stored (not added to the residual): a block may clear their outputs in passing."""
-        return (self.down, self.uq)
+        return (self.down, self.uq) if self.q_rank else (self.down,)
 
     def cache_spec(self):
         return KVSpec(1, self.kv_rank + self.rot_dim, self.window, planes=1)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         E, C, R = self.hidden, self.kv_rank, self.rot_dim
-        return {"dq": TensorSpec((self.q_rank, E)), "dq.norm": TensorSpec((self.q_rank,), "vector", init="one_plus_normal", std=0.01),
-                "uq": TensorSpec((self.q_width, self.q_rank)),
-                "dkv": TensorSpec((C + R, E)), "dkv.norm": TensorSpec((C,), "vector", init="one_plus_normal", std=0.01),
-                "uk": TensorSpec((self.heads * self.key_dim, C)), "uv": TensorSpec((self.v_width, C)),
-                "o": TensorSpec((E, self.v_width))}
+        specs = {"dkv": TensorSpec((C + R, E)), "dkv.norm": TensorSpec((C,), "vector", init="one_plus_normal", std=0.01),
+                 "uk": TensorSpec((self.heads * self.key_dim, C)), "uv": TensorSpec((self.v_width, C)),
+                 "o": TensorSpec((E, self.v_width))}
+        if self.q_rank:
+            specs.update({"dq": TensorSpec((self.q_rank, E)), "dq.norm": TensorSpec((self.q_rank,), "vector", init="one_plus_normal", std=0.01),
+                          "uq": TensorSpec((self.q_width, self.q_rank))})
+        else:
+            specs["q"] = TensorSpec((self.q_width, E))
+        if self.gate:
+            specs["g"] = TensorSpec((self.v_width, E))
+        return specs
+
+    def frequencies(self):
+        """(float32 frequencies [rot_dims / 2] rounded once from double, the factor on cosines and sines)."""
+        if self.rot_scaling is not None and self.rot_dims:
+            f, magnitude = blended_frequencies(self.rot_base, self.rot_dims, *self.rot_scaling)
+        else:
+            f, magnitude = power_frequencies(self.rot_base, self.rot_dims), 1.0
+        return f.astype(np.float32), float(magnitude)
 
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
         self.cleared_outputs = {}
         t = tensors
-        self.down = Linear(torch.cat([t["dq"], t["dkv"]], dim=0), precision)      # one product for both latents
-        self.uq, self.o = Linear(t["uq"], precision), Linear(t["o"], precision)
-        self.dq_norm = t["dq.norm"].to(torch.float32).contiguous()
+        # One product for everything that reads h: [query latent | key/value latent | rotated part], or without a query
+        # latent [key/value latent | rotated part | queries], then the gate's input.
+        stacked = [t["dq"], t["dkv"]] if self.q_rank else [t["dkv"], t["q"]]
+        if self.gate:
+            stacked.append(t["g"])
+        self.down = Linear(torch.cat(stacked, dim=0), precision)
+        self.o = Linear(t["o"], precision)
+        self.uq = Linear(t["uq"], precision) if self.q_rank else None
+        self.dq_norm = t["dq.norm"].to(torch.float32).contiguous() if self.q_rank else None
         self.dkv_norm = t["dkv.norm"].to(torch.float32).contiguous()
         self.w_uk = t["uk"].to(precision.act).contiguous()
         self.w_uv = t["uv"].to(precision.act).contiguous()
-        # f_i = base^(-2i / dims) in double precision, rounded once; the angle is the float product with the position.
-        i = np.arange(self.rot_dims // 2, dtype=np.float64)
-        freq = np.power(np.float64(self.rot_base), -2.0 * i / max(self.rot_dims, 1)).astype(np.float32)
+        # Frequencies in double precision, rounded once; the angle is the float product with the position.
+        freq, self.rot_magnitude = self.frequencies()
         self.freq = torch.from_numpy(freq).to(self.w_uk.device)
         self._sms = torch.cuda.get_device_properties(self.w_uk.device).multi_processor_count if self.w_uk.is_cuda else 148
 
@@ -109,11 +143,21 @@ class LatentAttention(Part):
                 and residual.dtype is torch.float32 and residual.is_contiguous() and tuple(residual.shape) == (rows, self.hidden)):
             raise runtime.KernelError("latent attention: rows of the path's type and the mixer's width, a float32 residual")
         group, cache = step.kv(cache_entry)
-        cq = torch.empty((rows, self.q_rank), dtype=self.precision.act, device=h.device)
         slots = group.slots if write_cache else torch.full((rows,), -1, dtype=torch.int32, device=h.device)
-        ops.latent_write(stored_product(self, self.down, h), self.q_rank, self.dq_norm, cq, self.dkv_norm, self.norm_eps, self.freq, step.positions,
-                         slots, cache, self.kv_rank, self.rot_dim)
-        q = stored_product(self, self.uq, cq)
+        halves, mag = self.pairing == "halves", self.rot_magnitude
+        proj = stored_product(self, self.down, h)
+        latents = self.q_rank + self.kv_rank + self.rot_dim
+        if self.q_rank:
+            cq = torch.empty((rows, self.q_rank), dtype=self.precision.act, device=h.device)
+            ops.latent_write(proj[:, :latents], self.q_rank, self.dq_norm, cq, self.dkv_norm, self.norm_eps, self.freq, step.positions,
+                             slots, cache, self.kv_rank, self.rot_dim, halves=halves, magnitude=mag)
+            q = stored_product(self, self.uq, cq)
+            gate_at = latents
+        else:
+            ops.latent_write(proj[:, :latents], 0, None, None, self.dkv_norm, self.norm_eps, self.freq, step.positions,
+                             slots, cache, self.kv_rank, self.rot_dim, halves=halves, magnitude=mag)
+            q = proj[:, latents:latents + self.q_width]
+            gate_at = latents + self.q_width
         o = torch.empty((rows, self.v_width), dtype=self.precision.act, device=h.device)
         # The tiled kernels hold a cache row in a warp's registers: rows of up to 768 values.
         tiles = None if self.precision.invariant or self.kv_rank + self.rot_dim > 768 else step.plan_ints(self)
@@ -122,10 +166,13 @@ class LatentAttention(Part):
             host_tiles, splits = self._tiling(step.host_row_count, step.max_context)
             ops.latent_attention_tiled(q, cache, self.w_uk, self.w_uv, o, self.freq, step.row_request, step.positions,
                                        group.block_tables, tiles, len(host_tiles), splits, self.heads, self.key_dim, self.rot_dim,
-                                       self.value_dim, self.kv_rank, group.page_size, self.window, self.scale, plain_cores=self.plain_cores)
+                                       self.value_dim, self.kv_rank, group.page_size, self.window, self.scale, plain_cores=self.plain_cores,
+                                       halves=halves, magnitude=mag)
         else:
             # One block per (row, head): the schedule follows the sizes alone (an invariant path, or a step without a plan).
             ops.latent_attention(q, cache, self.w_uk, self.w_uv, o, self.freq, step.row_request, step.positions, group.block_tables,
                                  self.heads, self.key_dim, self.rot_dim, self.value_dim, self.kv_rank, group.page_size, self.window,
-                                 self.scale)
+                                 self.scale, halves=halves, magnitude=mag)
+        if self.gate:
+            ops.sigmoid_gate_(o, proj[:, gate_at:gate_at + self.v_width])
         self.o(o, out=residual, accumulate=True)

@@ -16,6 +16,20 @@ width D and value width V:
 Sizes, the scale, whether q/k are normed, the rotation's constants, window and chunk are constructor arguments, and so
 are the tensors' roles.  The cache keeps what later rows can still see: pages wholly below the window or the chunk
 of the next position are given back.  Kernels: csrc/attention_split.cu.
+
+Options for designs that vary it (any of them makes the rows go through the general finishing kernel, `llmx_qkv_finish`):
+    bias True             q, k, v and the output product have biases (the tensor's role with ".b" added)
+    taps n > 1            a causal filter of n taps on each channel of q, k and v right after the product (roles
+                          "<q>.conv" ..., [channels, taps], last tap on the current token, zeros before the request's first
+                          token); the last n - 1 product rows of a request are its state (a second cache entry, a state
+                          slot of (n - 1) * channels floats)
+    pairing "neighbours"  rotation pair i is (2i, 2i + 1) instead of (i, i + rot_dims / 2)
+    qk_norm "after"       the per-head RMS norm comes after the rotation instead of before it
+    qk_norm_weight False  the norm has no weight
+    shared_kv True        the mixer has no key and value tensors: it reads the cache entry another layer's mixer of the
+                          same geometry wrote (the layer order names that entry and does not write it), with queries,
+                          filter state and everything else of its own
+With a filter the mixer's cache need is a pair (keys and values, filter state) and `forward` is handed a pair of entries.
 """
 from __future__ import annotations
 
@@ -26,7 +40,7 @@ import numpy as np
 import torch
 
 from .. import ops, runtime
-from ..cache.manager import KVSpec
+from ..cache.manager import KVSpec, StateSpec
 from ..weights.spec import TensorSpec
 from .base import Part, Precision, StepBatch
 from .linear import Linear, stored_product
@@ -36,7 +50,8 @@ class MaskedAttention(Part):
     def __init__(self, hidden: int, heads: int, kv_heads: int, key_dim: int, value_dim: int, scale: Optional[float] = None,
                  qk_norm_eps: Optional[float] = None, rot_dims: int = 0, rot_base: float = 10000.0, rot_factor: float = 1.0,
                  window: Optional[int] = None, chunk: Optional[int] = None,
-                 names=("q", "k", "v", "o", "q.norm", "k.norm")):
+                 names=("q", "k", "v", "o", "q.norm", "k.norm"), bias: bool = False, taps: int = 1, pairing: str = "halves",
+                 qk_norm: str = "before", qk_norm_weight: bool = True, shared_kv: bool = False):
         if heads % kv_heads:
             raise ValueError("attention: head count must be divisible by the key/value head count")
         if rot_dims % 2 or rot_dims > key_dim or rot_dims < 0:
@@ -49,20 +64,40 @@ class MaskedAttention(Part):
         self.window, self.chunk, self.names = window, chunk, tuple(names)
         self.q_width, self.k_width, self.v_width = self.heads * self.key_dim, self.kv_heads * self.key_dim, self.kv_heads * self.value_dim
         self.o_width = self.heads * self.value_dim
+        if pairing not in ("halves", "neighbours") or qk_norm not in ("before", "after") or taps < 1:
+            raise ValueError("attention: pairing is halves or neighbours, qk_norm before or after, the filter has at least one tap")
+        self.bias, self.taps, self.pairing, self.qk_norm = bool(bias), int(taps), pairing, qk_norm
+        self.qk_norm_weight, self.shared_kv = bool(qk_norm_weight), bool(shared_kv)
+        self.general = self.bias or self.taps > 1 or pairing != "halves" or qk_norm != "before" or not self.qk_norm_weight or self.shared_kv
+        self.channels = self.q_width + (0 if self.shared_kv else self.k_width + self.v_width)
+        self.defer_output_bias = False       # a block that reads the output through a kernel of its own may add the bias there
+        self.output_bias: Optional[torch.Tensor] = None
 
     def stored_products(self):
         return (self.qkv,)
 
     def cache_spec(self):
-        return KVSpec(self.kv_heads, self.key_dim + self.value_dim, self.window, planes=1, chunk=self.chunk)
+        kv = KVSpec(self.kv_heads, self.key_dim + self.value_dim, self.window, planes=1, chunk=self.chunk)
+        if self.taps > 1:
+            return (kv, StateSpec(((self.taps - 1) * self.channels,), "float32"))
+        return kv
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         q, k, v, o, qn, kn = self.names
-        specs = {q: TensorSpec((self.q_width, self.hidden)), k: TensorSpec((self.k_width, self.hidden)),
-                 v: TensorSpec((self.v_width, self.hidden)), o: TensorSpec((self.hidden, self.o_width))}
-        if self.qk_norm_eps is not None:
+        made = {q: self.q_width} if self.shared_kv else {q: self.q_width, k: self.k_width, v: self.v_width}
+        specs = {o: TensorSpec((self.hidden, self.o_width))}
+        for name, width in made.items():
+            specs[name] = TensorSpec((width, self.hidden))
+            if self.bias:
+                specs[name + ".b"] = TensorSpec((width,), "vector", init="normal", std=0.02)
+            if self.taps > 1:
+                specs[name + ".conv"] = TensorSpec((width, self.taps), std=0.3)
+        if self.bias:
+            specs[o + ".b"] = TensorSpec((self.hidden,), "vector", init="normal", std=0.02)
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             specs[qn] = TensorSpec((self.key_dim,), "vector", init="one_plus_normal", std=0.01)
-            specs[kn] = TensorSpec((self.key_dim,), "vector", init="one_plus_normal", std=0.01)
+            if not self.shared_kv:
+                specs[kn] = TensorSpec((self.key_dim,), "vector", init="one_plus_normal", std=0.01)
         return specs
 
     def frequencies(self) -> np.ndarray:
@@ -74,19 +109,30 @@ class MaskedAttention(Part):
         super().load(tensors, precision)
         self.cleared_outputs = {}
         q, k, v, o, qn, kn = self.names
-        self.qkv = Linear(torch.cat([tensors[q], tensors[k], tensors[v]], dim=0), precision)
+        made = [q] if self.shared_kv else [q, k, v]
+        self.qkv = Linear(torch.cat([tensors[n] for n in made], dim=0), precision)
         self.o = Linear(tensors[o], precision)
         self.q_norm = self.k_norm = None
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             self.q_norm = tensors[qn].to(torch.float32).contiguous()
-            self.k_norm = tensors[kn].to(torch.float32).contiguous()
+            self.k_norm = None if self.shared_kv else tensors[kn].to(torch.float32).contiguous()
+        self.in_bias = torch.cat([tensors[n + ".b"] for n in made]).to(torch.float32).contiguous() if self.bias else None
+        self.output_bias = tensors[o + ".b"].to(torch.float32).contiguous() if self.bias else None
+        self.taps_w = torch.cat([tensors[n + ".conv"] for n in made], dim=0).to(torch.float32).contiguous() if self.taps > 1 else None
         self.freq = torch.from_numpy(self.frequencies()).to(self.o.weight.device) if self.rot_dims else None
         self.tiled = precision.act is torch.bfloat16 and not precision.invariant and \
             ops.attention_tiled_fits(self.heads, self.kv_heads, self.key_dim, self.value_dim)
 
-    def forward(self, h: torch.Tensor, step: StepBatch, cache_entry: int, residual: torch.Tensor,
-                write_cache: bool = True) -> None:
+    def forward(self, h: torch.Tensor, step: StepBatch, cache_entry, residual: torch.Tensor, write_cache=True) -> None:
+        """`cache_entry`: the entry of keys and values, or with a filter the pair (keys and values, filter state);
+        `write_cache` likewise one flag or a pair (the filter's state is always written: it is the mixer's own)."""
         rows = h.shape[0]
+        state_entry = None
+        if isinstance(cache_entry, (tuple, list)):
+            cache_entry, state_entry = cache_entry
+        if isinstance(write_cache, (tuple, list)):
+            write_cache = write_cache[0]
+        write_cache = bool(write_cache) and not self.shared_kv
         if not (h.is_cuda and h.is_contiguous() and h.dtype is self.precision.act and tuple(h.shape) == (rows, self.hidden)
                 and residual.dtype is torch.float32 and residual.is_contiguous() and tuple(residual.shape) == (rows, self.hidden)):
             raise runtime.KernelError("attention: rows of the path's type and the mixer's width, a float32 residual")
@@ -94,8 +140,15 @@ class MaskedAttention(Part):
         proj = stored_product(self, self.qkv, h)                             # [rows, q | k | v], 32-bit
         q = torch.empty((rows, self.q_width), dtype=self.precision.act, device=h.device)
         slots = group.slots if write_cache else torch.full_like(group.slots, -1)
-        ops.qk_norm_rope_write(proj, self.heads, self.kv_heads, self.key_dim, self.value_dim, self.q_norm, self.k_norm,
-                               float(self.qk_norm_eps or 0.0), self.freq, step.positions, slots, q, cache)
+        if self.general:
+            ops.qkv_finish(proj, self.heads, 0 if self.shared_kv else self.kv_heads, self.key_dim, self.value_dim, step, q,
+                           cache=None if self.shared_kv else cache, slots=None if self.shared_kv else slots, bias=self.in_bias,
+                           taps_w=self.taps_w, state=step.state(state_entry) if self.taps > 1 else None,
+                           norm="none" if self.qk_norm_eps is None else self.qk_norm, q_weight=self.q_norm, k_weight=self.k_norm,
+                           eps=float(self.qk_norm_eps or 0.0), freq=self.freq, neighbours=self.pairing == "neighbours")
+        else:
+            ops.qk_norm_rope_write(proj, self.heads, self.kv_heads, self.key_dim, self.value_dim, self.q_norm, self.k_norm,
+                                   float(self.qk_norm_eps or 0.0), self.freq, step.positions, slots, q, cache)
         o = torch.empty((rows, self.o_width), dtype=self.precision.act, device=h.device)
         # Which kernel is a matter of speed only.  Steps that bring some request more than a few rows run the tiled
         # form (bfloat16, sizes it takes); others run the plain form, a row's keys cut into ranges when the rows alone
@@ -110,3 +163,5 @@ class MaskedAttention(Part):
             ops.attention_split(q, cache, o, step.row_request, step.positions, group.block_tables, self.heads, self.kv_heads,
                                 self.key_dim, self.value_dim, self.window, self.chunk, self.scale, splits=splits)
         self.o(o, out=residual, accumulate=True)
+        if self.output_bias is not None and not self.defer_output_bias:
+            ops.add_bias_(residual, self.output_bias)

@@ -66,21 +66,29 @@ class RMSNorm(Part):
 
 
 class LayerNorm(Part):
-    """y = (x - mean(x)) / sqrt(var(x) + eps) * w, var the mean of squared deviations; a weight and no bias; 32-bit
-    arithmetic (csrc/rowwise.cu, `llmx_layernorm`).  `role`: the weight's tensor role ("" names it by the part's
-    prefix alone).  The same interface as RMSNorm; it has no twin in the native runtime, so a block that holds it is
-    walked from Python."""
+    """y = (x - mean(x)) / sqrt(var(x) + eps) * w (+ b), var the mean of squared deviations; 32-bit arithmetic
+    (csrc/rowwise.cu, `llmx_layernorm_affine`).  `role`: the weight's tensor role ("" names it by the part's prefix
+    alone); `bias`: the role of a bias tensor, or None for a norm without one.  The same interface as RMSNorm; it has no
+    twin in the native runtime, so a block that holds it is walked from Python.  `add_into(residual, y, factor)`
+    norms y and adds factor times the result into the float32 residual in one kernel (the norm after a sublayer)."""
 
-    def __init__(self, width: int, eps: float, role: str = "weight"):
-        self.width, self.eps, self.role = int(width), float(eps), role
+    def __init__(self, width: int, eps: float, role: str = "weight", bias: Optional[str] = None):
+        self.width, self.eps, self.role, self.bias_role = int(width), float(eps), role, bias
+        if bias is not None and bias == role:
+            raise ValueError("layer norm: weight and bias need different roles")
         self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {self.role: TensorSpec((self.width,), "vector", init="one_plus_normal", std=0.01)}
+        specs = {self.role: TensorSpec((self.width,), "vector", init="one_plus_normal", std=0.01)}
+        if self.bias_role is not None:
+            specs[self.bias_role] = TensorSpec((self.width,), "vector", init="normal", std=0.02)
+        return specs
 
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
         self.weight = tensors[self.role].to(torch.float32).contiguous()
+        self.bias = tensors[self.bias_role].to(torch.float32).contiguous() if self.bias_role is not None else None
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
                 row_index: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
@@ -92,4 +100,9 @@ class LayerNorm(Part):
         if zero is not None and (zero.numel() % 4 or zero.data_ptr() % 16):
             zero.zero_()
             zero = None
-        return ops.layernorm(x, self.weight, self.eps, out, row_index, zero)
+        return ops.layernorm(x, self.weight, self.eps, out, row_index, zero, bias=self.bias)
+
+    def add_into(self, residual: torch.Tensor, y: torch.Tensor, factor: float, in_bias: Optional[torch.Tensor] = None) -> None:
+        """residual += factor * norm(y + in_bias); float32 rows."""
+        from .. import ops
+        ops.layernorm_add_(residual, y, self.weight, self.bias, self.eps, factor, in_bias=in_bias)

@@ -22,6 +22,31 @@ import torch
 from .base import Part
 
 
+def power_frequencies(base: float, dims: int) -> np.ndarray:
+    """f_i = base^(-2i / dims), i < dims / 2, in double precision."""
+    i = np.arange(dims // 2, dtype=np.float64)
+    return np.power(np.float64(base), -2.0 * i / max(dims, 1))
+
+
+def blended_frequencies(base: float, dims: int, factor: float, original: float, fast: float, slow: float):
+    """Frequencies for contexts longer than the `original` one a model was made for, and the factor on cosines and
+    sines that goes with them: pair i keeps f_i where it turns often within the original context and takes f_i / factor
+    where it turns rarely, with a linear ramp over the pair index in between.  With n(t) = dims ln(original / (2 pi t)) /
+    (2 ln base), the pair that makes t turns in `original` positions, the ramp runs from lo = max(floor(n(fast)), 0) to
+    hi = min(ceil(n(slow)), dims - 1): ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), and the frequency is
+    f_i / factor * ramp_i + f_i (1 - ramp_i).  The factor on cosines and sines is 0.1 ln(factor) + 1.
+    Returns (float64 frequencies [dims / 2], magnitude); the caller rounds once to 32-bit."""
+    f = power_frequencies(base, dims)
+
+    def pair_turning(turns: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+    lo = max(math.floor(pair_turning(fast)), 0)
+    hi = min(math.ceil(pair_turning(slow)), dims - 1)
+    ramp = np.clip((np.arange(dims // 2, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
 class NoPositionEncoding(Part):
     cos = None
     sin = None

@@ -93,3 +93,4 @@ def _ensure_builtin() -> None:
     from .models import qwen3 as _qwen3  # noqa: F401  (registers itself)
     from .models import buzetar as _buzetar  # noqa: F401
     from .models import kisepel as _kisepel  # noqa: F401
+    from .models import zamizen as _zamizen  # noqa: F401
