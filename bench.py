@@ -128,6 +128,9 @@ def reference_arm(args):
 # same width, depth, feed-forward width and head count.  `--design kisepel`: a Kisepel of as many layers (its three mixers
 # in turn; 16 experts of a quarter of the feed-forward width, two a token, beside a shared one of half the width, so that a
 # token meets as many feed-forward weights as in the dense models) beside the Buzetar of the same sizes.
+# `--design zamizen`: a Zamizen of as many layers (two latent layers, then a layer of grouped-query attention with a
+# four-tap filter; every second such layer reads the keys and values of the one before it) beside the two models that
+# have its kernels' nearest relatives: a Buzetar whose layers are all latent attention without a window, and a Qwen3.
 DESIGN_SIZES = {
     "w2048": dict(width=2048, heads=16, ff=6144, vocab=32768, q_rank=768, kv_rank=512, rot=64, window=2048, layers=6),
     "w4096": dict(width=4096, heads=32, ff=12288, vocab=32768, q_rank=1536, kv_rank=512, rot=64, window=4096, layers=3),
@@ -141,7 +144,7 @@ def design_bench(args) -> int:
     import statistics
     import torch
     from llmx_b200 import ops
-    from llmx_b200.config import BuzetarConfig, KisepelConfig, Qwen3Config
+    from llmx_b200.config import BuzetarConfig, KisepelConfig, Qwen3Config, ZamizenConfig
     from llmx_b200.engine import Engine, EngineOptions, StepEntry
     from llmx_b200.engine.decode_loop import DecodeSession
     torch.cuda.set_device(0)
@@ -174,8 +177,31 @@ def design_bench(args) -> int:
             {"type": "lightning", "mixer": {"heads": H, "dim": 128, "vdim": 128, "decay": decays}, "mlp": experts}]
         kis = KisepelConfig.from_dict({"architecture": "Kisepel", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
                                        "logit_scale": 1.0, "layers": [kis_kinds[i % 3] for i in range(L)]})
+        runs = (("kisepel", kis), ("buzetar", buz)) if args.design == "kisepel" else (("buzetar", buz), ("qwen3", qwen))
+        if args.design == "zamizen":
+            G = max(H // 4, 1)
+            latent = {"heads": H, "dim": 128, "rot_dim": z["rot"], "vdim": 128, "kv_rank": z["kv_rank"], "scale": (128 + z["rot"]) ** -0.5,
+                      "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+            gqa = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4, "rot": {"base": 1000000.0, "dims": 64}}
+            plain_mlp = {"kind": "dense", "ff": F}
+            zam_layers, last_own = [], None
+            for i in range(L):
+                if i % 3 != 2:
+                    zam_layers.append({"type": "latent_attention", "mixer": latent, "mlp": plain_mlp})
+                elif last_own is None:
+                    zam_layers.append({"type": "attention", "mixer": gqa, "mlp": plain_mlp})
+                    last_own = i
+                else:
+                    zam_layers.append({"type": "attention", "mixer": dict(gqa, kv_from=last_own), "mlp": plain_mlp})
+                    last_own = None
+            zam = ZamizenConfig.from_dict({"architecture": "Zamizen", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+                                           "layers": zam_layers})
+            all_latent = dict(kinds[1], mixer={k: v for k, v in kinds[1]["mixer"].items() if k != "mask"})
+            buz_latent = BuzetarConfig.from_dict({"architecture": "Buzetar", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+                                                  "logit_scale": 1.0, "layers": [all_latent] * L})
+            runs = (("zamizen", zam), ("buzetar_latent", buz_latent), ("qwen3", qwen))
         res = {}
-        for tag, cfg in ((("kisepel", kis), ("buzetar", buz)) if args.design == "kisepel" else (("buzetar", buz), ("qwen3", qwen))):
+        for tag, cfg in runs:
             per_request = -(-(C + 3 * args.steps + args.warmup + 64) // page) * page
             engine = Engine.from_config(cfg, seed=0, options=EngineOptions(dtype="bfloat16", kv_tokens=max(B * per_request, T + page),
                                                                            page_size=page, max_requests=B, record_after=2))
@@ -249,9 +275,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--only", choices=["decode", "prefill", "sample"], default=None,
                     help="run one part only (for profiling); the line then holds only that part")
-    ap.add_argument("--design", choices=["buzetar", "kisepel"], default=None,
+    ap.add_argument("--design", choices=["buzetar", "kisepel", "zamizen"], default=None,
                     help="instead of the default workload: prompt and decode throughput of this design at sizes that resemble a "
-                         "real model's layers, beside the closest other design of equal size (Buzetar beside Qwen3, Kisepel beside Buzetar; one JSON line of its own)")
+                         "real model's layers, beside the closest other design of equal size (Buzetar beside Qwen3, Kisepel beside Buzetar, "
+                         "Zamizen beside an all-latent Buzetar and Qwen3; one JSON line of its own)")
     ap.add_argument("--design-size", default=None, help="with --design: one of " + ", ".join(sorted(DESIGN_SIZES)) + " (default: all)")
     args = ap.parse_args()
     if args.impl == "reference":
