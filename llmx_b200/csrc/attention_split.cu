@@ -108,6 +108,7 @@ struct QkvFinish {
     int rot_pairs, neighbours;
     const int *positions, *slots;
     int heads, kv_heads, D, V, page_size, rows;
+    int planes;   // 1: a slot holds [key ; value] in one row of D + V; 2: keys and values in planes of their own (D = V)
 };
 
 template <typename QT, typename KVT>
@@ -192,9 +193,12 @@ qkv_finish_kernel(QkvFinish a, QT* __restrict__ q_out, KVT* __restrict__ cache) 
             for (int d = lane; d < D; d += 32) dst[d] = from_float<QT>(a.norm == 2 ? st[d] * rr * (w ? w[d] : 1.0f) : st[d]);
         } else {
             const int g = item - a.heads;
-            KVT* dst = cache + (((size_t)(slot / a.page_size) * a.kv_heads + g) * a.page_size + slot % a.page_size) * (size_t)(D + V);
+            const size_t page = slot / a.page_size, off = slot % a.page_size;
+            KVT* dst = a.planes == 2 ? cache + (((page * 2) * a.kv_heads + g) * a.page_size + off) * (size_t)D
+                                     : cache + ((page * a.kv_heads + g) * a.page_size + off) * (size_t)(D + V);
+            KVT* vdst = a.planes == 2 ? dst + (size_t)a.kv_heads * a.page_size * D : dst + D;
             for (int d = lane; d < D; d += 32) dst[d] = from_float<KVT>(a.norm == 2 ? st[d] * rr * (w ? w[d] : 1.0f) : st[d]);
-            for (int d = lane; d < V; d += 32) dst[D + d] = from_float<KVT>(filtered(v_off + g * V + d));
+            for (int d = lane; d < V; d += 32) vdst[d] = from_float<KVT>(filtered(v_off + g * V + d));
         }
         __syncwarp();                                                 // the stage is written again for the warp's next head
     }
@@ -564,14 +568,17 @@ LLMX_EXPORT int llmx_qk_norm_rope_write(const float* proj, int stride, const flo
 // float32 [channels, taps] or null (taps 1: no filter); state float32 [slots, slot_floats] with the filter's inputs at
 // conv_off; norm 0 / 1 / 2 = none / before / after the rotation, q_weight and k_weight float32 [D] or null; freq float32
 // [rot_pairs]; the rows' requests, their row ranges, histories and the slots read and written as a step gives them.
+// planes 1: cache [pages, 1, kv_heads, page_size, D + V]; planes 2 (D = V): cache [pages, 2, kv_heads, page_size, D], the
+// layout of the paged kernels with key and value planes.
 LLMX_EXPORT int llmx_qkv_finish(const float* proj, int stride, const float* bias, const float* taps_w, int taps, float* state,
                                 long long slot_floats, long long conv_off, const int* row_request, const int* row_start,
                                 const int* row_count, const int* history, const int* slot_in, const int* slot_out,
                                 const float* q_weight, const float* k_weight, int norm, float eps, const float* freq, int rot_pairs,
                                 int neighbours, const int* positions, const int* slots, void* q_out, int q_dtype, void* cache,
                                 int cache_dtype, int rows, int requests, int heads, int kv_heads, int D, int V, int page_size,
-                                cudaStream_t stream) {
+                                int planes, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (planes != 1 && !(planes == 2 && D == V)) return LLMX_ERR_BAD_ARGUMENT;
     if (D <= 0 || V <= 0 || heads <= 0 || kv_heads < 0 || D > 32 * MAX_PER_LANE || 2 * rot_pairs > D || rot_pairs < 0 ||
         (rot_pairs > 0 && freq == nullptr) || norm < 0 || norm > 2 || taps < 1 || (taps > 1 && (taps_w == nullptr || state == nullptr)) ||
         (kv_heads > 0 && (cache == nullptr || slots == nullptr || page_size <= 0)))
@@ -580,7 +587,7 @@ LLMX_EXPORT int llmx_qkv_finish(const float* proj, int stride, const float* bias
     if (taps > 1 && conv_off + (taps - 1) * channels > slot_floats) return LLMX_ERR_BAD_ARGUMENT;
     QkvFinish a{proj, stride, bias, taps_w, taps, state, slot_floats, conv_off, row_request, row_start, row_count, history, slot_in,
                 slot_out, q_weight, k_weight, norm, eps, freq, rot_pairs, neighbours, positions, slots, heads, kv_heads, D, V,
-                page_size > 0 ? page_size : 1, rows};
+                page_size > 0 ? page_size : 1, rows, planes};
     const dim3 grid(rows + (taps > 1 ? requests : 0));
     const bool cache16 = kv_heads > 0 && cache_dtype == LLMX_BF16;
     if (kv_heads > 0 && cache_dtype != LLMX_BF16 && cache_dtype != LLMX_F32) return LLMX_ERR_UNSUPPORTED;

@@ -467,7 +467,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
     const float* src = x + (size_t)(row_index ? row_index[r] : r) * width;
     OutT* dst = y + (size_t)r * width;
     float* sum = add_to ? add_to + (size_t)r * width : nullptr;
-    const float inv_n = 1.0f / (float)width;
+    const float n = (float)width;            // divided by, not multiplied with a rounded 1 / n: a row of equal values has deviations of exactly 0
     if (width <= LN_MAX * (int)blockDim.x) {
         float v[LN_MAX];
         float s = 0.0f;
@@ -477,7 +477,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
             v[k] = i < width ? src[i] + (in_bias ? in_bias[i] : 0.0f) : 0.0f;
             s += v[k];
         }
-        const float mean = block_sum(s, scratch) * inv_n;
+        const float mean = block_sum(s, scratch) / n;
         float q = 0.0f;
 #pragma unroll
         for (int k = 0; k < LN_MAX; ++k) {
@@ -486,7 +486,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
             v[k] = d;
             q = fmaf(d, d, q);
         }
-        const float rr = 1.0f / sqrtf(block_sum(q, scratch) * inv_n + eps);
+        const float rr = 1.0f / sqrtf(block_sum(q, scratch) / n + eps);
 #pragma unroll
         for (int k = 0; k < LN_MAX; ++k) {
             const int i = threadIdx.x + k * blockDim.x;
@@ -500,13 +500,13 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
     }
     float s = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) s += src[i] + (in_bias ? in_bias[i] : 0.0f);
-    const float mean = block_sum(s, scratch) * inv_n;
+    const float mean = block_sum(s, scratch) / n;
     float q = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float d = src[i] + (in_bias ? in_bias[i] : 0.0f) - mean;
         q = fmaf(d, d, q);
     }
-    const float rr = 1.0f / sqrtf(block_sum(q, scratch) * inv_n + eps);
+    const float rr = 1.0f / sqrtf(block_sum(q, scratch) / n + eps);
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float o = (src[i] + (in_bias ? in_bias[i] : 0.0f) - mean) * rr * w[i] + (b ? b[i] : 0.0f);
         if (sum) sum[i] = fmaf(mult, o, sum[i]);

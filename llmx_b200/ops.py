@@ -111,7 +111,7 @@ _SIGNATURES = {
                                           _p, ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _i, _i, _p],
     ("attention_split", "llmx_qk_norm_rope_write"): [_p, _i, _p, _p, _f, _p, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p],
     ("attention_split", "llmx_qkv_finish"): [_p, _i, _p, _p, _i, _p, ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _p, _p, _i,
-                                             _f, _p, _i, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p],
+                                             _f, _p, _i, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p],
     ("attention_split", "llmx_attention_split"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
     ("attention_split", "llmx_attention_tiled_fits"): [_i, _i, _i, _i],
     ("attention_split", "llmx_attention_tiled"): [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
@@ -583,7 +583,8 @@ def qkv_finish(proj: torch.Tensor, heads: int, kv_heads: int, key_dim: int, valu
     [slots, floats] at `conv_off` ([taps - 1][channels], read at the request's slot, written at its spare); an RMS norm
     per q and k head `norm` = "none" | "before" | "after" the rotation, with weights [D] or without; a rotation of the
     first 2 * len(freq) values of a head by position * freq[i], pairs (i, i + len(freq)) or `neighbours` (2i, 2i + 1);
-    queries to q_out [rows, heads * D], [k ; v] to cache [pages, 1, kv_heads, page, D + V] at `slots`.  `step`: the StepBatch."""
+    queries to q_out [rows, heads * D], [k ; v] to cache [pages, 1, kv_heads, page, D + V] at `slots`, or, where the cache
+    has planes of keys and of values, [pages, 2, kv_heads, page, D] (D = V), to those.  `step`: the StepBatch."""
     _cuda(bias, taps_w, state, q_weight, k_weight, freq, slots, q_out, cache)
     rows = proj.shape[0]
     channels = (heads + kv_heads) * key_dim + kv_heads * value_dim
@@ -601,9 +602,10 @@ def qkv_finish(proj: torch.Tensor, heads: int, kv_heads: int, key_dim: int, valu
         _need(state is not None and state.dtype == torch.float32 and state.dim() == 2
               and conv_off + (taps - 1) * channels <= state.shape[1], "qkv_finish: state slots too small for the filter's inputs")
     if kv_heads:
-        _need(cache is not None and slots is not None and cache.dim() == 5 and cache.shape[1] == 1 and cache.shape[2] == kv_heads
-              and cache.shape[4] == key_dim + value_dim and slots.dtype == torch.int32 and slots.numel() >= rows,
-              "qkv_finish: cache layout or slots do not fit")
+        _need(cache is not None and slots is not None and cache.dim() == 5 and cache.shape[2] == kv_heads and cache.is_contiguous()
+              and ((cache.shape[1] == 1 and cache.shape[4] == key_dim + value_dim)
+                   or (cache.shape[1] == 2 and key_dim == value_dim and cache.shape[4] == key_dim))
+              and slots.dtype == torch.int32 and slots.numel() >= rows, "qkv_finish: cache layout or slots do not fit")
     _need(freq is None or (freq.dtype == torch.float32 and 2 * freq.numel() <= key_dim), "qkv_finish: frequencies float32 [<= D / 2]")
     _check(_fn("attention_split", "llmx_qkv_finish")(
         _ptr(proj), proj.stride(0) if rows > 1 else proj.shape[1], _ptr(bias), _ptr(taps_w), taps, _ptr(state),
@@ -611,7 +613,8 @@ def qkv_finish(proj: torch.Tensor, heads: int, kv_heads: int, key_dim: int, valu
         _ptr(step.history), _ptr(step.state_slots), _ptr(step.state_slots_out), _ptr(q_weight), _ptr(k_weight),
         ("none", "before", "after").index(norm), float(eps), _ptr(freq), 0 if freq is None else freq.numel(), 1 if neighbours else 0,
         _ptr(step.positions), _ptr(slots), _ptr(q_out), _code(q_out), _ptr(cache), _code(cache) if cache is not None else F32, rows,
-        step.requests, heads, kv_heads, key_dim, value_dim, cache.shape[3] if cache is not None else 1, _stream()), "qkv_finish")
+        step.requests, heads, kv_heads, key_dim, value_dim, cache.shape[3] if cache is not None else 1,
+        cache.shape[1] if cache is not None else 1, _stream()), "qkv_finish")
 
 
 def attention_split(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row_request: torch.Tensor,

@@ -40,6 +40,23 @@ class NativePlan(PartPlan):
         self.plan.fill(list(histories), out)
 
 
+class AttentionShape(Part):
+    """The head counts, head width and window of an attention whose queries another part makes: no tensors, only the
+    runtime's launch plans for the paged kernels (`ops_attn.paged_attention` finds them in the step).  A mixer that runs
+    those kernels on queries of its own holds one as a child."""
+    native_planned = True
+
+    def __init__(self, heads: int, kv_heads: int, head_dim: int, window: Optional[int] = None):
+        self.heads, self.kv_heads, self.head_dim, self.window = int(heads), int(kv_heads), int(head_dim), window
+        self._native: Optional[NativeHandle] = None
+
+    @property
+    def native(self):
+        if self._native is None:
+            self._native = NativeHandle(runtime.lib().llmx_attention_shape(self.heads, self.kv_heads, self.head_dim, int(self.window or 0)))
+        return self._native.handle
+
+
 class Attention(Part):
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, position_encoding: Part,
                  qk_norm_eps: Optional[float] = None, window: Optional[int] = None,

@@ -30,6 +30,11 @@ Options for designs that vary it (any of them makes the rows go through the gene
                           same geometry wrote (the layer order names that entry and does not write it), with queries,
                           filter state and everything else of its own
 With a filter the mixer's cache need is a pair (keys and values, filter state) and `forward` is handed a pair of entries.
+
+Where keys and values are equally wide, nothing cuts the keys into chunks and the path is bfloat16, the mixer keeps its
+keys and values in planes of their own, [pages, 2, kv_heads, page, D], and its attention is the paged kernels' (split-KV
+decode, tcgen05 prompt tiles: `ops_attn.paged_attention`), whatever finished its queries; a layer that reads another's
+keys decides the same way, having the same geometry.  Which kernels run changes no result beyond rounding.
 """
 from __future__ import annotations
 
@@ -70,14 +75,23 @@ class MaskedAttention(Part):
         self.qk_norm_weight, self.shared_kv = bool(qk_norm_weight), bool(shared_kv)
         self.general = self.bias or self.taps > 1 or pairing != "halves" or qk_norm != "before" or not self.qk_norm_weight or self.shared_kv
         self.channels = self.q_width + (0 if self.shared_kv else self.k_width + self.v_width)
+        # Whether the paged kernels can serve this geometry (decided for good in `load`, which knows the path's type).
+        self.paged_shape = None
+        if self.key_dim == self.value_dim and self.chunk is None and self.key_dim in (64, 128) and self.heads // self.kv_heads <= 16:
+            from .attention import AttentionShape
+            self.paged_shape = AttentionShape(self.heads, self.kv_heads, self.key_dim, self.window)
+        self.paged = False
         self.defer_output_bias = False       # a block that reads the output through a kernel of its own may add the bias there
         self.output_bias: Optional[torch.Tensor] = None
 
     def stored_products(self):
         return (self.qkv,)
 
+    def children(self):
+        return {"paged": self.paged_shape} if self.paged_shape is not None else {}
+
     def cache_spec(self):
-        kv = KVSpec(self.kv_heads, self.key_dim + self.value_dim, self.window, planes=1, chunk=self.chunk)
+        kv = KVSpec(self.kv_heads, self.key_dim, self.window) if self.paged else KVSpec(self.kv_heads, self.key_dim + self.value_dim, self.window, planes=1, chunk=self.chunk)
         if self.taps > 1:
             return (kv, StateSpec(((self.taps - 1) * self.channels,), "float32"))
         return kv
@@ -120,6 +134,7 @@ class MaskedAttention(Part):
         self.output_bias = tensors[o + ".b"].to(torch.float32).contiguous() if self.bias else None
         self.taps_w = torch.cat([tensors[n + ".conv"] for n in made], dim=0).to(torch.float32).contiguous() if self.taps > 1 else None
         self.freq = torch.from_numpy(self.frequencies()).to(self.o.weight.device) if self.rot_dims else None
+        self.paged = self.paged_shape is not None and precision.act is torch.bfloat16 and not precision.invariant
         self.tiled = precision.act is torch.bfloat16 and not precision.invariant and \
             ops.attention_tiled_fits(self.heads, self.kv_heads, self.key_dim, self.value_dim)
 
@@ -140,7 +155,7 @@ class MaskedAttention(Part):
         proj = stored_product(self, self.qkv, h)                             # [rows, q | k | v], 32-bit
         q = torch.empty((rows, self.q_width), dtype=self.precision.act, device=h.device)
         slots = group.slots if write_cache else torch.full_like(group.slots, -1)
-        if self.general:
+        if self.general or self.paged:
             ops.qkv_finish(proj, self.heads, 0 if self.shared_kv else self.kv_heads, self.key_dim, self.value_dim, step, q,
                            cache=None if self.shared_kv else cache, slots=None if self.shared_kv else slots, bias=self.in_bias,
                            taps_w=self.taps_w, state=step.state(state_entry) if self.taps > 1 else None,
@@ -153,7 +168,10 @@ class MaskedAttention(Part):
         # Which kernel is a matter of speed only.  Steps that bring some request more than a few rows run the tiled
         # form (bfloat16, sizes it takes); others run the plain form, a row's keys cut into ranges when the rows alone
         # would not fill the device.
-        if self.tiled and step.max_row_count > 4 and cache.dtype is torch.bfloat16:
+        if self.paged:
+            from .. import ops_attn
+            ops_attn.paged_attention(q, o, step, cache_entry, self.heads, self.kv_heads, self.key_dim, self.window, self.scale)
+        elif self.tiled and step.max_row_count > 4 and cache.dtype is torch.bfloat16:
             ops.attention_tiled(q, cache, o, step, group.block_tables, self.heads, self.kv_heads, self.key_dim, self.value_dim,
                                 self.window, self.chunk, self.scale)
         else:
