@@ -208,6 +208,7 @@ def design_bench(args) -> int:
             vocab = z["vocab"]
             prompt = torch.randint(0, vocab, (T,), generator=host_gen).tolist()
             times = []
+            print(f"[bench] {name} {tag}: prompt", file=sys.stderr, flush=True)
             for i in range(3 + 5):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -223,6 +224,7 @@ def design_bench(args) -> int:
             pf_ms = statistics.median(times)
             r = {"prefill_tok_s": round(T * 1e3 / pf_ms, 1), "prefill_ms": round(pf_ms, 3),
                  "prefill_ms_by_kernel": {k: round(v[1], 4) for k, v in sorted(kt.by_function.items(), key=lambda kv: -kv[1][1])}}
+            print(f"[bench] {name} {tag}: decode", file=sys.stderr, flush=True)
             rids = [("bench", i) for i in range(B)]
             for rid in rids:                                     # room for the history without running it (zeros: a step's cost
                 rc = engine.cache.new_request(rid)               # depends on how much it reads, not on what)

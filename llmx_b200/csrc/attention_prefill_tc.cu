@@ -106,7 +106,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                        const int* __restrict__ history, const int* __restrict__ block_tables, int table_stride,
                        int heads, int kv_heads, int window, float scale_log2, int n_req, int max_blocks, int item_tiles,
                        int key_splits, float* __restrict__ partial, int* error_word) {
-    pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + SMEM_TILES);
@@ -166,6 +165,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Dependents may start arriving only now that this block holds its tensor memory: a dependent block that allocated
+    // its own first and then waited for this kernel would keep a block of this kernel waiting for columns for ever.
+    pdl_trigger();
     pdl_wait();
 
     // ---- The work: items (request, kv head, block of 2 x 128 / ratio new rows), the blocks with the most keys first.

@@ -146,7 +146,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                const HeadsEpilogue hp) {
     // HEADS: `map_w` is the tokens' map and N their number, `map_a` the weight's and M its rows.
     using cfg = Cfg<BN, DUAL>;
-    pdl_trigger();      // the next kernel's blocks may start arriving; they wait for this one to finish
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles = smem;
@@ -191,6 +190,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Dependents may start arriving only now that this block holds its tensor memory: a dependent block that allocated
+    // its own first and then waited for this kernel would keep a block of this kernel waiting for columns for ever.
+    pdl_trigger();
     // Barriers, tensor memory and descriptors are ready.  The weights are written by no kernel, so the
     // producer fetches its first stages of them at once; whatever another kernel writes (the activations,
     // the output) is touched only after pdl_wait(), when the kernel before has finished.

@@ -173,7 +173,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_wide, const __grid_c
                     void* __restrict__ C_, int wide_rows, int narrow_rows, int K, int mode, int splits, int group,
                     int tail, int* error_word, const HeadsEpilogue hp) {
     using cfg = PairCfg<BN, FORM>;
-    pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* tiles = smem;
@@ -219,6 +218,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_wide, const __grid_c
     cluster_sync();           // both blocks' barriers exist before either signals the other
     tc::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Dependents may start arriving only now that this block holds its tensor memory: a dependent block that allocated
+    // its own first and then waited for this kernel would keep a block of this kernel waiting for columns for ever.
+    pdl_trigger();
     pdl_wait();               // the activations and the output belong to the kernels before
 
     if (warp == 0) {
