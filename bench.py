@@ -153,6 +153,18 @@ def design_bench(args) -> int:
     page, T, B, C = 16, args.prefill_tokens, args.batch, args.context
     out = {"design": args.design, "dtype": "bf16", "data": "synthetic", "prefill_tokens": T, "batch": B, "context": C,
            "steps": args.steps, "warmup": args.warmup, "sizes": {}}
+
+    def finished(event, what: str, limit_s: float = 120.0) -> None:
+        """Waits for `event` on the host by polling; work that has not ended after `limit_s` is reported (one JSON line
+        with what was measured so far) and the process leaves at once, since its context cannot be torn down in order."""
+        t0 = time.time()
+        while not event.query():
+            if time.time() - t0 > limit_s:
+                out["stalled"] = what
+                print(json.dumps(out), flush=True)
+                print(f"[bench] {what} did not end within {limit_s:.0f} s", file=sys.stderr, flush=True)
+                os._exit(4)
+            time.sleep(0.0005)
     for name in (args.design_size.split(",") if args.design_size else sorted(DESIGN_SIZES)):
         z = DESIGN_SIZES[name]
         E, H, F, L = z["width"], z["heads"], z["ff"], z["layers"]
@@ -214,6 +226,7 @@ def design_bench(args) -> int:
                 e0.record()
                 engine.step([StepEntry("prefill", prompt, [T - 1])])
                 e1.record()
+                finished(e1, f"{name} {tag}: prompt step {i}")
                 torch.cuda.synchronize()
                 engine.end("prefill")
                 if i >= 3:
@@ -246,6 +259,7 @@ def design_bench(args) -> int:
             for _ in range(args.steps):
                 session.step(tokens)
             e1.record()
+            finished(e1, f"{name} {tag}: decode steps")
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / args.steps
             r.update(decode_tok_s=round(B * 1e3 / ms, 1), decode_ms_per_step=round(ms, 4), gpu_launches=ops.launch_count() - launches0)

@@ -14,6 +14,7 @@
 // merged in warp order, so the order of a row's sums depends on its own keys only.
 #include "common.cuh"
 #include <math.h>
+#include <algorithm>
 
 namespace {
 constexpr int WARPS = 4;
@@ -91,7 +92,8 @@ qk_write_kernel(const float* __restrict__ proj, int stride, const float* __restr
 //         a rotation of pair i < rot_pairs by position * freq[i]: the pair is (i, i + rot_pairs), or with `neighbours`
 //         (2i, 2i + 1)
 //   q -> q_out, [k ; v] -> the row's cache slot (kv_heads 0: the rows hold queries only, another layer's keys are read)
-// One block per row, a warp per head; blocks beyond the rows write the requests' new filter inputs.
+// A row's heads are spread over the blocks (x, 0..gridDim.y - 1), a warp per head; blocks whose x lies beyond the rows write
+// the requests' new filter inputs, the channels spread likewise.
 struct QkvFinish {
     const float* proj;
     int stride;
@@ -117,6 +119,7 @@ qkv_finish_kernel(QkvFinish a, QT* __restrict__ q_out, KVT* __restrict__ cache) 
     pdl_trigger();
     pdl_wait();
     __shared__ float stage[4][32 * MAX_PER_LANE];
+    __shared__ float turn[2][16 * MAX_PER_LANE];
     const int keep = a.taps - 1;
     const int D = a.D, V = a.V;
     const int channels = (a.heads + a.kv_heads) * D + a.kv_heads * V;
@@ -128,7 +131,7 @@ qkv_finish_kernel(QkvFinish a, QT* __restrict__ q_out, KVT* __restrict__ cache) 
         if (n <= 0) return;
         const float* old = a.state + (size_t)a.slot_in[r] * a.slot_floats + a.conv_off;
         float* fresh = a.state + (size_t)a.slot_out[r] * a.slot_floats + a.conv_off;
-        for (int c = threadIdx.x; c < channels; c += blockDim.x)
+        for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x)
             for (int s = 0; s < keep; ++s) {
                 const int ii = n - keep + s;
                 float x = 0.0f;
@@ -158,9 +161,12 @@ qkv_finish_kernel(QkvFinish a, QT* __restrict__ q_out, KVT* __restrict__ cache) 
         }
         return y;
     };
+    // The row's cosines and sines once for all of its heads.
+    for (int i = threadIdx.x; i < a.rot_pairs; i += blockDim.x) sincosf(pos * a.freq[i], &turn[1][i], &turn[0][i]);
+    __syncthreads();
     float* st = stage[warp];
     const int v_off = (a.heads + a.kv_heads) * D;
-    for (int item = warp; item < a.heads + a.kv_heads; item += warps) {
+    for (int item = blockIdx.y * warps + warp; item < a.heads + a.kv_heads; item += gridDim.y * warps) {
         const bool is_q = item < a.heads;
         if (!is_q && slot < 0) continue;                              // a row whose cache write is skipped
         const float* w = is_q ? a.q_weight : a.k_weight;
@@ -176,8 +182,7 @@ qkv_finish_kernel(QkvFinish a, QT* __restrict__ q_out, KVT* __restrict__ cache) 
         for (int i = lane; i < a.rot_pairs; i += 32) {
             const int ia = a.neighbours ? 2 * i : i, ib = a.neighbours ? 2 * i + 1 : i + a.rot_pairs;
             const float u = st[ia], v = st[ib];
-            float sn, cs;
-            sincosf(pos * a.freq[i], &sn, &cs);
+            const float cs = turn[0][i], sn = turn[1][i];
             st[ia] = u * cs - v * sn;
             st[ib] = v * cs + u * sn;
         }
@@ -588,7 +593,7 @@ LLMX_EXPORT int llmx_qkv_finish(const float* proj, int stride, const float* bias
     QkvFinish a{proj, stride, bias, taps_w, taps, state, slot_floats, conv_off, row_request, row_start, row_count, history, slot_in,
                 slot_out, q_weight, k_weight, norm, eps, freq, rot_pairs, neighbours, positions, slots, heads, kv_heads, D, V,
                 page_size > 0 ? page_size : 1, rows, planes};
-    const dim3 grid(rows + (taps > 1 ? requests : 0));
+    const dim3 grid(rows + (taps > 1 ? requests : 0), std::min((heads + kv_heads + 3) / 4, 64));
     const bool cache16 = kv_heads > 0 && cache_dtype == LLMX_BF16;
     if (kv_heads > 0 && cache_dtype != LLMX_BF16 && cache_dtype != LLMX_F32) return LLMX_ERR_UNSUPPORTED;
     if (q_dtype == LLMX_BF16 && cache16) launch_kernel(qkv_finish_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(128), 0, stream, a, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache);
