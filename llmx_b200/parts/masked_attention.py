@@ -31,10 +31,13 @@ Options for designs that vary it (any of them makes the rows go through the gene
                           filter state and everything else of its own
 With a filter the mixer's cache need is a pair (keys and values, filter state) and `forward` is handed a pair of entries.
 
-Where keys and values are equally wide, nothing cuts the keys into chunks and the path is bfloat16, the mixer keeps its
-keys and values in planes of their own, [pages, 2, kv_heads, page, D], and its attention is the paged kernels' (split-KV
-decode, tcgen05 prompt tiles: `ops_attn.paged_attention`), whatever finished its queries; a layer that reads another's
-keys decides the same way, having the same geometry.  Which kernels run changes no result beyond rounding.
+    rounded_weights True  the design lets softmax weights enter the product with the values rounded to bfloat16 (the
+                          kernels here keep them to 24 bits: the plain form in 32-bit arithmetic, the tiled form as three
+                          bfloat16 parts).  Then, where keys and values are equally wide (64 or 128), nothing cuts the keys
+                          into chunks and the path is bfloat16, the mixer keeps keys and values in planes of their own,
+                          [pages, 2, kv_heads, page, D], and its attention is the paged kernels' (split-KV decode, tcgen05
+                          prompt tiles: `ops_attn.paged_attention`), whatever finished its queries; a layer that reads
+                          another's keys decides the same way, having the same geometry.  Off by default.
 """
 from __future__ import annotations
 
@@ -56,7 +59,7 @@ class MaskedAttention(Part):
                  qk_norm_eps: Optional[float] = None, rot_dims: int = 0, rot_base: float = 10000.0, rot_factor: float = 1.0,
                  window: Optional[int] = None, chunk: Optional[int] = None,
                  names=("q", "k", "v", "o", "q.norm", "k.norm"), bias: bool = False, taps: int = 1, pairing: str = "halves",
-                 qk_norm: str = "before", qk_norm_weight: bool = True, shared_kv: bool = False):
+                 qk_norm: str = "before", qk_norm_weight: bool = True, shared_kv: bool = False, rounded_weights: bool = False):
         if heads % kv_heads:
             raise ValueError("attention: head count must be divisible by the key/value head count")
         if rot_dims % 2 or rot_dims > key_dim or rot_dims < 0:
@@ -77,7 +80,7 @@ class MaskedAttention(Part):
         self.channels = self.q_width + (0 if self.shared_kv else self.k_width + self.v_width)
         # Whether the paged kernels can serve this geometry (decided for good in `load`, which knows the path's type).
         self.paged_shape = None
-        if self.key_dim == self.value_dim and self.chunk is None and self.key_dim in (64, 128) and self.heads // self.kv_heads <= 16:
+        if rounded_weights and self.key_dim == self.value_dim and self.chunk is None and self.key_dim in (64, 128) and self.heads // self.kv_heads <= 16:
             from .attention import AttentionShape
             self.paged_shape = AttentionShape(self.heads, self.kv_heads, self.key_dim, self.window)
         self.paged = False

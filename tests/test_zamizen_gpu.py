@@ -217,9 +217,9 @@ def test_whole_models_under_every_cutting_bfloat16(tmp_path, which):
     print("bfloat16 error / scale:", which, measured)
 
 
-# R: attention whose keys and values are equally wide and of a width the paged kernels take (64 and 128), so that in
-# bfloat16 its keys and values lie in planes of their own and the split-KV decode and the prompt-tile kernels run;
-# a lender and a borrower among them, a latent layer between.  In float32 the same model runs the plain form.
+# R: attention whose keys and values are equally wide, of the widths (64 and 128) for which the framework has kernels
+# that round softmax weights to bfloat16.  Zamizen keeps its weights in 32-bit, so those kernels must not serve it on
+# either path; a lender and a borrower among the layers, a latent layer between.
 MODEL_R = config([attention(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.2, conv=3, rot_dims=32),
                   latent(ff=None),
                   attention(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.2, conv=2, rot_dims=32, kv_from=0, ff=None),
@@ -232,7 +232,7 @@ def test_equally_wide_keys_and_values_under_every_cutting(tmp_path, dtype):
     cfg = MODEL_R
     w = make_folder(str(tmp_path), cfg, seed=21, dtype=torch.bfloat16 if dtype == "bfloat16" else torch.float32)
     engine = Engine.from_dir(str(tmp_path), EngineOptions(dtype=dtype, kv_tokens=64, page_size=16, max_requests=2))
-    assert [b.mixer.paged for b in engine.model.blocks if hasattr(b.mixer, "paged")] == [dtype == "bfloat16"] * 3
+    assert [b.mixer.paged for b in engine.model.blocks if hasattr(b.mixer, "paged")] == [False] * 3
     del engine
     measured = run_cuttings(str(tmp_path), cfg, w, dtype, [50, 3, 77, 20, 1, 64, 133], BF16_BUDGET["P"] if dtype == "bfloat16" else 1e-4, page=16)
     print(dtype, "error / scale:", measured)
