@@ -212,7 +212,8 @@ def design_bench(args) -> int:
             buz_latent = BuzetarConfig.from_dict({"architecture": "Buzetar", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
                                                   "logit_scale": 1.0, "layers": [all_latent] * L})
             runs = (("zamizen", zam), ("buzetar_latent", buz_latent), ("qwen3", qwen))
-        res = {}
+        res = {"config": dict(z)}
+        out["sizes"][name] = res                                # filled as the arms end, so that a run that stops early says what it has
         for tag, cfg in runs:
             per_request = -(-(C + 3 * args.steps + args.warmup + 64) // page) * page
             engine = Engine.from_config(cfg, seed=0, options=EngineOptions(dtype="bfloat16", kv_tokens=max(B * per_request, T + page),
@@ -271,8 +272,6 @@ def design_bench(args) -> int:
             import gc
             gc.collect()
             torch.cuda.empty_cache()
-        res["config"] = dict(z)
-        out["sizes"][name] = res
     print(json.dumps(out))
     return 0
 
