@@ -238,6 +238,22 @@ def test_equally_wide_keys_and_values_under_every_cutting(tmp_path, dtype):
     print(dtype, "error / scale:", measured)
 
 
+def test_the_attention_part_with_rounded_weights_runs_the_paged_kernels(tmp_path, monkeypatch):
+    """`MaskedAttention(rounded_weights=True)`, which no design sets: the same model built with it keeps keys and values
+    in planes and runs the paged kernels in bfloat16; it agrees with the plain implementation to the bfloat16 budget."""
+    import functools
+    import llmx_b200.models.zamizen as builder
+    from llmx_b200.engine import Engine, EngineOptions
+    from llmx_b200.parts import MaskedAttention
+    monkeypatch.setattr(builder, "MaskedAttention", functools.partial(MaskedAttention, rounded_weights=True))
+    cfg = MODEL_R
+    w = make_folder(str(tmp_path), cfg, seed=21, dtype=torch.bfloat16)
+    engine = Engine.from_dir(str(tmp_path), EngineOptions(dtype="bfloat16", kv_tokens=64, page_size=16, max_requests=2))
+    assert [b.mixer.paged for b in engine.model.blocks if hasattr(b.mixer, "paged")] == [True] * 3
+    del engine
+    run_cuttings(str(tmp_path), cfg, w, "bfloat16", [50, 3, 77, 20, 1, 64, 133], BF16_BUDGET["P"], page=16)
+
+
 def test_a_request_in_a_batch_equals_the_request_alone(tmp_path):
     """Unequal requests in one step (a long portion, a short one, single tokens after history) against each alone."""
     from llmx_b200.engine import StepEntry
