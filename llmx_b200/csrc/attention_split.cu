@@ -5,6 +5,7 @@
 // weight of D values shared by the heads (optional), a rotation of the first 2 * rot_half values of every query and
 // key head (value i pairs with value i + rot_half; the angle is position * freq[i], made in 32-bit here, so there is
 // no table whose length bounds the context), queries to `q_out`, keys and values to the row's cache slot.
+// Designs vary the softmax (`AttnExtras`: a cap on the scores, a sink in the denominator, values rotated by position).
 // `llmx_attention_split` is the plain form of the attention: one block per (row, head); a row at position p reads the
 // keys lo..p of its own request, where lo is the larger of p - window + 1 (window > 0) and the start of p's chunk,
 // floor(p / chunk) * chunk (chunk > 0: positions are counted from the start of the request, so chunks do not move
@@ -88,7 +89,9 @@ qk_write_kernel(const float* __restrict__ proj, int stride, const float* __restr
 //                                                     token; inputs of earlier steps come from the request's state slot,
 //                                                     which holds the last taps - 1 values of u ([taps - 1][channels] at
 //                                                     `conv_off`); the step's last ones go to the slot the step writes
-//   q, k: a norm per head (RMS over D, weights of D values or none) before the rotation (norm 1) or after it (norm 2),
+//   q, k: a norm per head (RMS over D, weights of D values or none) before the rotation (norm 1) or after it (norm 2), or
+//         one RMS norm over all of a row's queries and one over all of its keys, before they are split into heads and
+//         rotated, with weights of heads * D and kv_heads * D values (norm 3),
 //         a rotation of pair i < rot_pairs by position * freq[i]: the pair is (i, i + rot_pairs), or with `neighbours`
 //         (2i, 2i + 1)
 //   q -> q_out, [k ; v] -> the row's cache slot (kv_heads 0: the rows hold queries only, another layer's keys are read)
@@ -111,6 +114,8 @@ struct QkvFinish {
     const int *positions, *slots;
     int heads, kv_heads, D, V, page_size, rows;
     int planes;   // 1: a slot holds [key ; value] in one row of D + V; 2: keys and values in planes of their own (D = V)
+    float rot_mag;        // a factor on the cosines and sines of the q/k rotation
+    const float* vfreq;   // [V / 2] or null: values are rotated by their position over all of V, in the q/k pairing
 };
 
 template <typename QT, typename KVT>
@@ -162,7 +167,34 @@ qkv_finish_kernel(QkvFinish a, QT* __restrict__ q_out, KVT* __restrict__ cache) 
         return y;
     };
     // The row's cosines and sines once for all of its heads.
-    for (int i = threadIdx.x; i < a.rot_pairs; i += blockDim.x) sincosf(pos * a.freq[i], &turn[1][i], &turn[0][i]);
+    for (int i = threadIdx.x; i < a.rot_pairs; i += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * a.freq[i], &sn, &cs);
+        turn[0][i] = cs * a.rot_mag;
+        turn[1][i] = sn * a.rot_mag;
+    }
+    // Norm 3: the root mean square of all of the row's queries, and of all of its keys.  Every block of the row makes both,
+    // with the same threads in the same order.
+    __shared__ float whole[2], whole_part[4];
+    if (a.norm == 3) {
+        for (int which = 0; which < (a.kv_heads > 0 ? 2 : 1); ++which) {
+            const int c_lo = which == 0 ? 0 : a.heads * D, c_hi = which == 0 ? a.heads * D : (a.heads + a.kv_heads) * D;
+            float ss = 0.0f;
+            for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) {
+                const float v = filtered(c);
+                ss = fmaf(v, v, ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) whole_part[warp] = ss;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                float t = 0.0f;
+                for (int w = 0; w < warps; ++w) t += whole_part[w];
+                whole[which] = 1.0f / sqrtf(t / (float)(c_hi - c_lo) + a.eps);
+            }
+            __syncthreads();
+        }
+    }
     __syncthreads();
     float* st = stage[warp];
     const int v_off = (a.heads + a.kv_heads) * D;
@@ -177,6 +209,11 @@ qkv_finish_kernel(QkvFinish a, QT* __restrict__ q_out, KVT* __restrict__ cache) 
             for (int d = lane; d < D; d += 32) ss = fmaf(st[d], st[d], ss);
             const float rr = 1.0f / sqrtf(warp_sum(ss) / (float)D + a.eps);
             for (int d = lane; d < D; d += 32) st[d] = st[d] * rr * (w ? w[d] : 1.0f);
+            __syncwarp();
+        } else if (a.norm == 3) {
+            const float rr = whole[is_q ? 0 : 1];
+            const float* wh = w ? w + (size_t)(is_q ? item : item - a.heads) * D : nullptr;
+            for (int d = lane; d < D; d += 32) st[d] = st[d] * rr * (wh ? wh[d] : 1.0f);
             __syncwarp();
         }
         for (int i = lane; i < a.rot_pairs; i += 32) {
@@ -203,9 +240,59 @@ qkv_finish_kernel(QkvFinish a, QT* __restrict__ q_out, KVT* __restrict__ cache) 
                                      : cache + ((page * a.kv_heads + g) * a.page_size + off) * (size_t)(D + V);
             KVT* vdst = a.planes == 2 ? dst + (size_t)a.kv_heads * a.page_size * D : dst + D;
             for (int d = lane; d < D; d += 32) dst[d] = from_float<KVT>(a.norm == 2 ? st[d] * rr * (w ? w[d] : 1.0f) : st[d]);
-            for (int d = lane; d < V; d += 32) vdst[d] = from_float<KVT>(filtered(v_off + g * V + d));
+            if (a.vfreq == nullptr) {
+                for (int d = lane; d < V; d += 32) vdst[d] = from_float<KVT>(filtered(v_off + g * V + d));
+            } else {
+                __syncwarp();                                         // the key has left the stage
+                for (int d = lane; d < V; d += 32) st[d] = filtered(v_off + g * V + d);
+                __syncwarp();
+                for (int i = lane; i < V / 2; i += 32) {
+                    const int ia = a.neighbours ? 2 * i : i, ib = a.neighbours ? 2 * i + 1 : i + V / 2;
+                    float sn, cs;
+                    sincosf(pos * a.vfreq[i], &sn, &cs);
+                    const float u = st[ia], v = st[ib];
+                    vdst[ia] = from_float<KVT>(u * cs - v * sn);
+                    vdst[ib] = from_float<KVT>(v * cs + u * sn);
+                }
+            }
         }
         __syncwarp();                                                 // the stage is written again for the warp's next head
+    }
+}
+
+// What a design may add to the softmax attention below.
+//   softcap > 0: score <- softcap * tanh(score / softcap), after the scale
+//   sink_mode 1: exp(sink[head]) joins the softmax's denominator (a learned number per head that has no key and no value);
+//             2: the same with 0 for every head (one is added to the denominator)
+//   vfreq [V / 2]: the cached values were rotated by their positions over all of V (pair m by position * vfreq[m]; pairs
+//             (m, m + V / 2), or with v_neighbours (2m, 2m + 1)); a row's output is turned back by its own position
+struct AttnExtras {
+    float softcap;
+    const float* sink;
+    int sink_mode;
+    const float* vfreq;
+    int v_neighbours;
+};
+
+// The factor on the weighted sum and the whole denominator, given the keys' maximum m and sum l (relative to m).
+__device__ __forceinline__ float finish_softmax(float m, float l, const AttnExtras& x, int head) {
+    if (x.sink_mode == 0) return 1.0f / l;
+    const float sk = x.sink_mode == 1 ? x.sink[head] : 0.0f;
+    const float top = fmaxf(m, sk);
+    const float f = m == -INFINITY ? 0.0f : expf(m - top);
+    return f / (l * f + expf(sk - top));
+}
+
+// The row's output in `o` (float, V values, written by this warp's lanes) turned back by the row's position, to `orow`.
+template <typename QT>
+__device__ __forceinline__ void write_turned_back(const float* o, QT* orow, int V, float pos, const AttnExtras& x, int lane) {
+    for (int i = lane; i < V / 2; i += 32) {
+        const int ia = x.v_neighbours ? 2 * i : i, ib = x.v_neighbours ? 2 * i + 1 : i + V / 2;
+        float sn, cs;
+        sincosf(pos * x.vfreq[i], &sn, &cs);
+        const float u = o[ia], v = o[ib];
+        orow[ia] = from_float<QT>(u * cs + v * sn);
+        orow[ib] = from_float<QT>(v * cs - u * sn);
     }
 }
 
@@ -214,10 +301,11 @@ __global__ void __launch_bounds__(WARPS * 32)
 attention_split_kernel(const QT* __restrict__ q, const KVT* __restrict__ cache, QT* __restrict__ out,
                        const int* __restrict__ row_request, const int* __restrict__ positions,
                        const int* __restrict__ block_tables, int table_stride, int heads, int kv_heads, int D, int V,
-                       int page_size, int window, int chunk, float scale, int splits, float* __restrict__ partial) {
+                       int page_size, int window, int chunk, float scale, int splits, float* __restrict__ partial,
+                       AttnExtras extras) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float smem[];  // WARPS * (V + 2)
+    extern __shared__ float smem[];  // WARPS * (V + 2), then V for the output before it is turned back
     const int row = blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = h / (heads / kv_heads);
@@ -255,6 +343,7 @@ attention_split_kernel(const QT* __restrict__ q, const KVT* __restrict__ cache, 
             if (d < D) s = fmaf(qv[i], to_float(kp[d]), s);
         }
         s = warp_sum(s) * scale;
+        if (extras.softcap > 0.0f) s = extras.softcap * tanhf(s / extras.softcap);
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first key
         const float e = expf(s - m_new);
@@ -301,10 +390,17 @@ attention_split_kernel(const QT* __restrict__ q, const KVT* __restrict__ cache, 
             return;
         }
         QT* orow = out + ((size_t)row * heads + h) * V;
+        const float inv = finish_softmax(mm, ll, extras, h);
+        float* turned = smem + WARPS * (V + 2);
         for (int d = lane; d < V; d += 32) {
             float o = 0.0f;
             for (int w = 0; w < WARPS; ++w) o += smem[w * (V + 2) + d] * f[w];
-            orow[d] = from_float<QT>(o / ll);
+            if (extras.vfreq) turned[d] = o * inv;
+            else orow[d] = from_float<QT>(o * inv);
+        }
+        if (extras.vfreq) {
+            __syncwarp();
+            write_turned_back(turned, orow, V, (float)pos, extras, lane);
         }
     }
 }
@@ -312,11 +408,14 @@ attention_split_kernel(const QT* __restrict__ q, const KVT* __restrict__ cache, 
 // The ranges' partial states of one (row, head), merged in range order.  One warp a (row, head).
 template <typename QT>
 __global__ void __launch_bounds__(128)
-attention_merge_kernel(const float* __restrict__ partial, QT* __restrict__ out, int items, int V, int splits) {
+attention_merge_kernel(const float* __restrict__ partial, QT* __restrict__ out, int items, int V, int splits, int heads,
+                       const int* __restrict__ positions, AttnExtras extras) {
     pdl_trigger();
     pdl_wait();
+    extern __shared__ float merge_smem[];            // 4 * V: a warp's output before it is turned back
     const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (item >= items) return;
+    float* turned = merge_smem + (threadIdx.x >> 5) * V;
     const float* p = partial + (size_t)item * splits * (V + 2);
     float mm = -INFINITY;
     for (int s = 0; s < splits; ++s) mm = fmaxf(mm, p[(size_t)s * (V + 2) + V]);
@@ -325,13 +424,19 @@ attention_merge_kernel(const float* __restrict__ partial, QT* __restrict__ out, 
         const float ms = p[(size_t)s * (V + 2) + V];
         ll += ms == -INFINITY ? 0.0f : p[(size_t)s * (V + 2) + V + 1] * expf(ms - mm);
     }
+    const float inv = finish_softmax(mm, ll, extras, item % heads);
     for (int d = lane; d < V; d += 32) {
         float o = 0.0f;
         for (int s = 0; s < splits; ++s) {
             const float ms = p[(size_t)s * (V + 2) + V];
             if (ms != -INFINITY) o += p[(size_t)s * (V + 2) + d] * expf(ms - mm);
         }
-        out[(size_t)item * V + d] = from_float<QT>(o / ll);
+        if (extras.vfreq) turned[d] = o * inv;
+        else out[(size_t)item * V + d] = from_float<QT>(o * inv);
+    }
+    if (extras.vfreq) {
+        __syncwarp();
+        write_turned_back(turned, out + (size_t)item * V, V, (float)positions[item / heads], extras, lane);
     }
 }
 
@@ -375,7 +480,8 @@ __global__ void __launch_bounds__(128)
 attention_tiled_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                        __nv_bfloat16* __restrict__ out, const int* __restrict__ row_start, const int* __restrict__ row_count,
                        const int* __restrict__ history, const int* __restrict__ block_tables, int table_stride, int requests,
-                       int heads, int kv_heads, int D, int V, int page_size, int window, int chunk, float scale, int r_pad) {
+                       int heads, int kv_heads, int D, int V, int page_size, int window, int chunk, float scale, int r_pad,
+                       AttnExtras extras) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char tl_smem[];
@@ -478,7 +584,9 @@ attention_tiled_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             for (int i = 0; i < 4; ++i) {
                 const int hf = i >> 1, key = kt0 + 8 * n + 2 * tig + (i & 1);
                 const bool seen = valid[hf] && key >= lo[hf] && key <= pos[hf];
-                s[n][i] = seen ? s[n][i] * scale : -INFINITY;
+                float sc = s[n][i] * scale;
+                if (extras.softcap > 0.0f) sc = extras.softcap * tanhf(sc / extras.softcap);
+                s[n][i] = seen ? sc : -INFINITY;
                 mx[hf] = fmaxf(mx[hf], s[n][i]);
             }
         float corr[2], base[2];
@@ -527,6 +635,40 @@ attention_tiled_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             }
         }
     }
+    if (extras.vfreq) {
+        // Rotated values: the normed outputs meet in shared memory (the key buffers are free now), and every row is turned
+        // back by its own position on the way out.
+        __syncthreads();
+        float* fo = reinterpret_cast<float*>(KV);                    // [TL_ROWS][V]
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            l[hf] += __shfl_xor_sync(0xffffffffu, l[hf], 1);
+            l[hf] += __shfl_xor_sync(0xffffffffu, l[hf], 2);
+            const int row = 16 * warp + gid + 8 * hf;
+            const float inv = valid[hf] ? finish_softmax(m[hf], l[hf], extras, g * ratio + row % r_pad) : 0.0f;
+#pragma unroll
+            for (int nv = 0; nv < VN_MAX; ++nv)
+                if (nv < vn) {
+                    fo[(size_t)row * V + 8 * nv + 2 * tig] = o[nv][2 * hf] * inv;
+                    fo[(size_t)row * V + 8 * nv + 2 * tig + 1] = o[nv][2 * hf + 1] * inv;
+                }
+        }
+        __syncthreads();
+        const int half = V / 2;
+        for (int i = threadIdx.x; i < TL_ROWS * half; i += 128) {
+            const int row = i / half, pm = i - row * half;
+            const int tk = row / r_pad, hd = row % r_pad;
+            if (tk >= n_tok || hd >= ratio) continue;
+            const int ia = extras.v_neighbours ? 2 * pm : pm, ib = extras.v_neighbours ? 2 * pm + 1 : pm + half;
+            float sn, cs;
+            sincosf((float)(hist + t0 + tk) * extras.vfreq[pm], &sn, &cs);
+            const float u = fo[(size_t)row * V + ia], v = fo[(size_t)row * V + ib];
+            __nv_bfloat16* orow = out + ((size_t)(a0 + t0 + tk) * heads + (size_t)g * ratio + hd) * V;
+            orow[ia] = __float2bfloat16_rn(u * cs + v * sn);
+            orow[ib] = __float2bfloat16_rn(v * cs - u * sn);
+        }
+        return;
+    }
 #pragma unroll
     for (int hf = 0; hf < 2; ++hf) {
         l[hf] += __shfl_xor_sync(0xffffffffu, l[hf], 1);
@@ -534,7 +676,7 @@ attention_tiled_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         if (!valid[hf]) continue;
         const int row = 16 * warp + gid + 8 * hf;
         const int tk = row / r_pad, hd = row % r_pad;
-        const float inv = 1.0f / l[hf];
+        const float inv = finish_softmax(m[hf], l[hf], extras, g * ratio + hd);
         __nv_bfloat16* orow = out + ((size_t)(a0 + t0 + tk) * heads + (size_t)g * ratio + hd) * V;
 #pragma unroll
         for (int nv = 0; nv < VN_MAX; ++nv)
@@ -571,8 +713,10 @@ LLMX_EXPORT int llmx_qk_norm_rope_write(const float* proj, int stride, const flo
 // The general form of the above (see `QkvFinish`): proj float32 [rows, stride] = q (heads * D) | k (kv_heads * D) | v (kv_heads
 // * V), kv_heads 0 for rows of queries alone (then `cache` and `slots` are not used); bias float32 [channels] or null; taps_w
 // float32 [channels, taps] or null (taps 1: no filter); state float32 [slots, slot_floats] with the filter's inputs at
-// conv_off; norm 0 / 1 / 2 = none / before / after the rotation, q_weight and k_weight float32 [D] or null; freq float32
-// [rot_pairs]; the rows' requests, their row ranges, histories and the slots read and written as a step gives them.
+// conv_off; norm 0 / 1 / 2 = none / before / after the rotation, q_weight and k_weight float32 [D] or null; norm 3 = over the
+// whole of a row's queries and of its keys before the rotation, weights float32 [heads * D] and [kv_heads * D]; freq float32
+// [rot_pairs], cosines and sines times rot_mag; vfreq float32 [V / 2] or null: values rotated over all of V by their position;
+// the rows' requests, their row ranges, histories and the slots read and written as a step gives them.
 // planes 1: cache [pages, 1, kv_heads, page_size, D + V]; planes 2 (D = V): cache [pages, 2, kv_heads, page_size, D], the
 // layout of the paged kernels with key and value planes.
 LLMX_EXPORT int llmx_qkv_finish(const float* proj, int stride, const float* bias, const float* taps_w, int taps, float* state,
@@ -581,18 +725,18 @@ LLMX_EXPORT int llmx_qkv_finish(const float* proj, int stride, const float* bias
                                 const float* q_weight, const float* k_weight, int norm, float eps, const float* freq, int rot_pairs,
                                 int neighbours, const int* positions, const int* slots, void* q_out, int q_dtype, void* cache,
                                 int cache_dtype, int rows, int requests, int heads, int kv_heads, int D, int V, int page_size,
-                                int planes, cudaStream_t stream) {
+                                int planes, float rot_mag, const float* vfreq, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (planes != 1 && !(planes == 2 && D == V)) return LLMX_ERR_BAD_ARGUMENT;
     if (D <= 0 || V <= 0 || heads <= 0 || kv_heads < 0 || D > 32 * MAX_PER_LANE || 2 * rot_pairs > D || rot_pairs < 0 ||
-        (rot_pairs > 0 && freq == nullptr) || norm < 0 || norm > 2 || taps < 1 || (taps > 1 && (taps_w == nullptr || state == nullptr)) ||
+        (rot_pairs > 0 && freq == nullptr) || norm < 0 || norm > 3 || taps < 1 || (vfreq != nullptr && (V % 2 || V > 32 * MAX_PER_LANE)) || (taps > 1 && (taps_w == nullptr || state == nullptr)) ||
         (kv_heads > 0 && (cache == nullptr || slots == nullptr || page_size <= 0)))
         return LLMX_ERR_BAD_ARGUMENT;
     const long long channels = (long long)(heads + kv_heads) * D + (long long)kv_heads * V;
     if (taps > 1 && conv_off + (taps - 1) * channels > slot_floats) return LLMX_ERR_BAD_ARGUMENT;
     QkvFinish a{proj, stride, bias, taps_w, taps, state, slot_floats, conv_off, row_request, row_start, row_count, history, slot_in,
                 slot_out, q_weight, k_weight, norm, eps, freq, rot_pairs, neighbours, positions, slots, heads, kv_heads, D, V,
-                page_size > 0 ? page_size : 1, rows, planes};
+                page_size > 0 ? page_size : 1, rows, planes, rot_mag, vfreq};
     const dim3 grid(rows + (taps > 1 ? requests : 0), std::min((heads + kv_heads + 3) / 4, 64));
     const bool cache16 = kv_heads > 0 && cache_dtype == LLMX_BF16;
     if (kv_heads > 0 && cache_dtype != LLMX_BF16 && cache_dtype != LLMX_F32) return LLMX_ERR_UNSUPPORTED;
@@ -610,17 +754,20 @@ LLMX_EXPORT int llmx_qkv_finish(const float* proj, int stride, const float* bias
 LLMX_EXPORT int llmx_attention_split(const void* q, int q_dtype, const void* cache, int cache_dtype, void* out,
                                      const int* row_request, const int* positions, const int* block_tables,
                                      int table_stride, int rows, int heads, int kv_heads, int D, int V, int page_size,
-                                     int window, int chunk, float scale, int splits, float* partial, cudaStream_t stream) {
+                                     int window, int chunk, float scale, int splits, float* partial, float softcap,
+                                     const float* sink, int sink_mode, const float* vfreq, int v_neighbours, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (sink_mode < 0 || sink_mode > 2 || (sink_mode == 1 && sink == nullptr) || (vfreq != nullptr && V % 2)) return LLMX_ERR_BAD_ARGUMENT;
+    const AttnExtras extras{softcap, sink, sink_mode, vfreq, v_neighbours};
     if (D <= 0 || V <= 0 || D > 32 * MAX_PER_LANE || V > 32 * MAX_PER_LANE || heads % kv_heads || heads > 65535)
         return LLMX_ERR_UNSUPPORTED;
     if (splits < 1 || splits > 64 || (splits > 1 && partial == nullptr)) return LLMX_ERR_BAD_ARGUMENT;
     dim3 grid(rows, heads, splits);
-    const size_t shmem = (size_t)WARPS * (V + 2) * sizeof(float);
+    const size_t shmem = ((size_t)WARPS * (V + 2) + V) * sizeof(float);
 #define LLMX_SPLIT(QT, KVT)                                                                                            \
     launch_kernel(attention_split_kernel<QT, KVT>, dim3(grid), dim3(WARPS * 32), shmem, stream, (const QT*)q,         \
                   (const KVT*)cache, (QT*)out, row_request, positions, block_tables, table_stride, heads, kv_heads, D, \
-                  V, page_size, window, chunk, scale, splits, partial)
+                  V, page_size, window, chunk, scale, splits, partial, extras)
     if (q_dtype == LLMX_BF16 && cache_dtype == LLMX_BF16) LLMX_SPLIT(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == LLMX_BF16 && cache_dtype == LLMX_F32) LLMX_SPLIT(__nv_bfloat16, float);
     else if (q_dtype == LLMX_F32 && cache_dtype == LLMX_BF16) LLMX_SPLIT(float, __nv_bfloat16);
@@ -631,9 +778,9 @@ LLMX_EXPORT int llmx_attention_split(const void* q, int q_dtype, const void* cac
     if (status || splits == 1) return status;
     const int items = rows * heads;
     if (q_dtype == LLMX_BF16)
-        launch_kernel(attention_merge_kernel<__nv_bfloat16>, dim3((items + 3) / 4), dim3(128), 0, stream, (const float*)partial, (__nv_bfloat16*)out, items, V, splits);
+        launch_kernel(attention_merge_kernel<__nv_bfloat16>, dim3((items + 3) / 4), dim3(128), (size_t)4 * V * sizeof(float), stream, (const float*)partial, (__nv_bfloat16*)out, items, V, splits, heads, positions, extras);
     else
-        launch_kernel(attention_merge_kernel<float>, dim3((items + 3) / 4), dim3(128), 0, stream, (const float*)partial, (float*)out, items, V, splits);
+        launch_kernel(attention_merge_kernel<float>, dim3((items + 3) / 4), dim3(128), (size_t)4 * V * sizeof(float), stream, (const float*)partial, (float*)out, items, V, splits, heads, positions, extras);
     return launch_status();
 }
 
@@ -650,8 +797,11 @@ LLMX_EXPORT int llmx_attention_tiled_fits(int heads, int kv_heads, int D, int V)
 LLMX_EXPORT int llmx_attention_tiled(const void* q, const void* cache, void* out, const int* row_start, const int* row_count,
                                      const int* history, const int* block_tables, int table_stride, int rows, int requests,
                                      int heads, int kv_heads, int D, int V, int page_size, int window, int chunk, float scale,
+                                     float softcap, const float* sink, int sink_mode, const float* vfreq, int v_neighbours,
                                      cudaStream_t stream) {
     if (rows <= 0 || requests <= 0) return 0;
+    if (sink_mode < 0 || sink_mode > 2 || (sink_mode == 1 && sink == nullptr)) return LLMX_ERR_BAD_ARGUMENT;
+    const AttnExtras extras{softcap, sink, sink_mode, vfreq, v_neighbours};
     if (!llmx_attention_tiled_fits(heads, kv_heads, D, V) || kv_heads > 65535) return LLMX_ERR_UNSUPPORTED;
     int r_pad = 1;
     while (r_pad < heads / kv_heads) r_pad *= 2;
@@ -663,7 +813,7 @@ LLMX_EXPORT int llmx_attention_tiled(const void* q, const void* cache, void* out
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_tiled_kernel<VN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         launch_kernel(attention_tiled_kernel<VN>, dim3(grid), dim3(128), smem, stream, (const __nv_bfloat16*)q,          \
                       (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, row_start, row_count, history, block_tables,    \
-                      table_stride, requests, heads, kv_heads, D, V, page_size, window, chunk, scale, r_pad);           \
+                      table_stride, requests, heads, kv_heads, D, V, page_size, window, chunk, scale, r_pad, extras);   \
         return launch_status();                                                                                           \
     } while (0)
     if (V <= 64) LLMX_TILED(8);

@@ -1,4 +1,5 @@
-// A mixture of experts whose routing is a table: token id -> the `top` experts that token uses (no router product).
+// A mixture of experts whose routing is a table: token id -> the `top` experts that token uses (no router product), or
+// row of the step -> experts, as a router (`llmx_moe_router`) wrote it on the device.
 //
 // A step's rows are sorted by expert on the device, so that nothing about the routing is read on the host and a step
 // can be recorded and replayed.  A *pair* is (row, k): row r with the k-th expert of its token, numbered r * top + k.
@@ -37,7 +38,7 @@ route_kernel(const int* __restrict__ token_ids, const int* __restrict__ table, i
         const int p = p0 + threadIdx.x;
         bool mine = false;
         if (p < pairs) {
-            const int tok = token_ids[p / top];
+            const int tok = token_ids ? token_ids[p / top] : p / top;      // no ids: the table has a row for each row of the step
             mine = tok >= 0 && tok < vocab && table[(size_t)tok * top + p % top] == e;
         }
         const unsigned ballot = __ballot_sync(0xffffffffu, mine);
@@ -319,7 +320,7 @@ moe_few_kernel(const __nv_bfloat16* __restrict__ a, int a_div, const __nv_bfloat
     extern __shared__ __align__(16) unsigned char few_smem[];
     uint4* row = reinterpret_cast<uint4*>(few_smem);                 // the pair's row, K bfloat16
     const int p = blockIdx.x;
-    const int tok = token_ids[p / top];
+    const int tok = token_ids ? token_ids[p / top] : p / top;
     const int e = (tok >= 0 && tok < vocab) ? table[(size_t)tok * top + p % top] : -1;
     if (e < 0 || e >= experts) return;
     const uint4* src = reinterpret_cast<const uint4*>(a + (size_t)(p / a_div) * K);
@@ -359,8 +360,98 @@ __global__ void combine_kernel(const float* __restrict__ y, float* __restrict__ 
     x[i] = fmaf(weight, s, x[i]);
 }
 
+// x[row] += factor * sum_k pair_weight[row * top + k] * y[row * top + k], k in increasing order.
+__global__ void combine_weighted_kernel(const float* __restrict__ y, float* __restrict__ x, const float* __restrict__ pair_weight,
+                                        int top, int width, float factor, long long n) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long row = i / width;
+    const int c = (int)(i % width);
+    float s = 0.0f;
+    for (int k = 0; k < top; ++k) s = fmaf(pair_weight[row * top + k], y[((size_t)row * top + k) * width + c], s);
+    x[i] = fmaf(factor, s, x[i]);
+}
+
+// A router: logits z = h W^T + b in 32-bit (h may be bfloat16; the weights are 32-bit), the `top` largest (the lower index
+// first among equals), and as weights the softmax over the chosen logits alone.  `extra` more rows of W after the experts'
+// give one number a row each through a sigmoid (a gate on a part that runs beside the experts).  One block a row; a warp
+// makes one logit, lanes in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(128)
+router_kernel(const T* __restrict__ h, const float* __restrict__ w, const float* __restrict__ bias, int K, int experts, int top,
+              int extra, int* __restrict__ choice, float* __restrict__ weight, float* __restrict__ gate) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float router_z[];                    // [experts + extra]
+    const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* x = h + (size_t)row * K;
+    for (int e = warp; e < experts + extra; e += 4) {
+        const float* we = w + (size_t)e * K;
+        float s = 0.0f;
+        for (int k = lane; k < K; k += 32) s = fmaf(to_float(x[k]), we[k], s);
+        s = warp_sum(s);
+        if (lane == 0) router_z[e] = s + ((bias && e < experts) ? bias[e] : 0.0f);
+    }
+    __syncthreads();
+    if (threadIdx.x < extra) gate[(size_t)row * extra + threadIdx.x] = 1.0f / (1.0f + expf(-router_z[experts + threadIdx.x]));
+    if (threadIdx.x != 0) return;
+    float zmax = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        int best = -1;
+        float bz = 0.0f;
+        for (int e = 0; e < experts; ++e) {
+            const float z = router_z[e];
+            if (z != z) continue;                            // a logit that is no number is never chosen
+            bool taken = false;
+            for (int j = 0; j < k; ++j) taken |= choice[(size_t)row * top + j] == e;
+            if (!taken && (best < 0 || z > bz)) best = e, bz = z;
+        }
+        if (best < 0) best = 0, bz = -INFINITY;
+        choice[(size_t)row * top + k] = best;
+        weight[(size_t)row * top + k] = bz;
+        if (k == 0) zmax = bz;
+    }
+    float sum = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        const float e = expf(weight[(size_t)row * top + k] - zmax);
+        weight[(size_t)row * top + k] = e;
+        sum += e;
+    }
+    for (int k = 0; k < top; ++k) weight[(size_t)row * top + k] /= sum;
+}
+
 inline int max_tiles(int pairs, int experts, int tile_rows) { return (pairs + tile_rows - 1) / tile_rows + experts; }
 }  // namespace
+
+// h [rows, K] of `dtype`; w float32 [experts + extra, K]; bias float32 [experts] or null; choice int32 [rows, top]; weight float32
+// [rows, top]; gate float32 [rows, extra] (extra 0: not used).
+LLMX_EXPORT int llmx_moe_router(const void* h, int dtype, const float* w, const float* bias, int rows, int K, int experts, int top,
+                                int extra, int* choice, float* weight, float* gate, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (K <= 0 || experts <= 0 || top <= 0 || top > experts || extra < 0 || extra > 128 || (extra > 0 && gate == nullptr) ||
+        (size_t)(experts + extra) * sizeof(float) > 48 * 1024)
+        return LLMX_ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)(experts + extra) * sizeof(float);
+    if (dtype == LLMX_BF16)
+        launch_kernel(router_kernel<__nv_bfloat16>, dim3(rows), dim3(128), smem, stream, (const __nv_bfloat16*)h, w, bias, K, experts, top, extra, choice, weight, gate);
+    else if (dtype == LLMX_F32)
+        launch_kernel(router_kernel<float>, dim3(rows), dim3(128), smem, stream, (const float*)h, w, bias, K, experts, top, extra, choice, weight, gate);
+    else
+        return LLMX_ERR_UNSUPPORTED;
+    return launch_status();
+}
+
+// x [rows, width] += factor * sum over k of pair_weight[rows * top] * y [rows * top, width], k in increasing order.
+LLMX_EXPORT int llmx_moe_combine_weighted(const float* y, float* x, const float* pair_weight, int rows, int top, int width,
+                                          float factor, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (pair_weight == nullptr) return LLMX_ERR_BAD_ARGUMENT;
+    const long long n = (long long)rows * width;
+    launch_kernel(combine_weighted_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, y, x, pair_weight, top, width, factor, n);
+    return launch_status();
+}
 
 // The pairs a tile holds for the products' two forms: the routing cuts the lists for the form that will run.
 LLMX_EXPORT int llmx_moe_tile_rows(int tensor_cores) { return tensor_cores ? TC_ROWS : TILE_ROWS; }

@@ -731,3 +731,233 @@ LLMX_EXPORT int llmx_add(float* x, const float* y, long long n, cudaStream_t str
     launch_kernel(add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, y, n);
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// RMS norm in groups, with the mixer's input filter in the same launch.
+//   h[c]  = x[c] / sqrt(mean(part(c)^2) + eps) * w[c]        the row in `groups` equal consecutive parts, each with its own
+//                                                            root mean square
+//   hm[c] = h[c] + sum_j taps_w[c, j] h_(t - taps + 1 + j)[c]  a causal filter over the request's rows, per channel; the last
+//                                                            tap lies on the row itself, rows before the request's first
+//                                                            token are zeros
+// A block makes one row.  The filter needs the normed values of the taps - 1 rows before: those of the same step are made
+// again from x (the same arithmetic, so the same bits), those of earlier steps lie in the request's state slot, which
+// holds its last taps - 1 normed rows ([taps - 1][width] floats at `state_off`); the step's last ones go to the slot the
+// step writes.  One warp makes the sum of squares of one (row, part), lanes in a fixed order.  Blocks beyond the rows:
+// one a request, copying what the new state keeps of the old one when the step brings fewer than taps - 1 rows; then
+// blocks that clear `zero`.  With `row_index` the rows are gathered (no filter then).
+struct GroupNormConv {
+    const float* x;
+    const float* w;
+    int width, groups;
+    float eps;
+    const int* row_index;
+    int rows;
+    const float* taps_w;
+    int taps;
+    float* state;
+    long long slot_floats, state_off;
+    const int *row_request, *row_start, *row_count, *history, *slot_in, *slot_out;
+    int requests;
+    float* zero;
+    long long zero_count;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+group_norm_conv_kernel(GroupNormConv a, OutT* __restrict__ h, OutT* __restrict__ hm) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float gnc_rstd[];                    // [taps][groups]
+    const int keep = a.taps - 1, width = a.width;
+    const int state_blocks = keep > 0 ? a.requests : 0;
+    if ((int)blockIdx.x >= a.rows + state_blocks) {
+        float4* z = reinterpret_cast<float4*>(a.zero);
+        const long long n4 = a.zero_count >> 2;
+        const long long blocks = gridDim.x - a.rows - state_blocks;
+        for (long long i = (long long)(blockIdx.x - a.rows - state_blocks) * blockDim.x + threadIdx.x; i < n4; i += blocks * blockDim.x)
+            z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        return;
+    }
+    if ((int)blockIdx.x >= a.rows) {
+        const int q = blockIdx.x - a.rows;
+        const int n = a.row_count[q], hist = a.history[q];
+        if (n <= 0 || n >= keep) return;
+        const float* old = a.state + (size_t)a.slot_in[q] * a.slot_floats + a.state_off;
+        float* fresh = a.state + (size_t)a.slot_out[q] * a.slot_floats + a.state_off;
+        for (int s = 0; s < keep - n; ++s) {
+            const int ii = n - keep + s;                    // < 0: a row of an earlier step, or before the request
+            for (int c = threadIdx.x; c < width; c += blockDim.x)
+                fresh[(size_t)s * width + c] = hist + ii >= 0 ? old[(size_t)(keep + ii) * width + c] : 0.0f;
+        }
+        return;
+    }
+    const int r = blockIdx.x;
+    const int src_row = a.row_index ? a.row_index[r] : r;
+    int first = 0, i0 = 0, hist = 0, n = 0;
+    const float* old = nullptr;
+    float* fresh = nullptr;
+    if (keep > 0) {
+        const int q = a.row_request[r];
+        first = a.row_start[q];
+        i0 = r - first;
+        hist = a.history[q];
+        n = a.row_count[q];
+        old = a.state + (size_t)a.slot_in[q] * a.slot_floats + a.state_off;
+        fresh = a.state + (size_t)a.slot_out[q] * a.slot_floats + a.state_off;
+    }
+    const int part = width / a.groups;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int item = warp; item < a.taps * a.groups; item += warps) {
+        const int j = item / a.groups, g = item - j * a.groups;
+        const int ii = i0 - keep + j;
+        if (j < keep && ii < 0) continue;                    // not a row of this step
+        const float* xr = a.x + (size_t)(j == keep ? src_row : first + ii) * width + (size_t)g * part;
+        float ss = 0.0f;
+        for (int c = lane; c < part; c += 32) ss = fmaf(xr[c], xr[c], ss);
+        ss = warp_sum(ss);
+        if (lane == 0) gnc_rstd[item] = 1.0f / sqrtf(ss / (float)part + a.eps);
+    }
+    __syncthreads();
+    const float* xrow = a.x + (size_t)src_row * width;
+    const int s_new = i0 - (n - keep);                       // the place of this row in the state the step leaves
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const int g = c / part;
+        const float wc = a.w[c];
+        const float cur = xrow[c] * gnc_rstd[keep * a.groups + g] * wc;
+        h[(size_t)r * width + c] = from_float<OutT>(cur);
+        if (keep > 0) {
+            float acc = 0.0f;
+            for (int j = 0; j < keep; ++j) {
+                const int ii = i0 - keep + j;
+                float v = 0.0f;
+                if (ii >= 0) v = a.x[(size_t)(first + ii) * width + c] * gnc_rstd[j * a.groups + g] * wc;
+                else if (hist + ii >= 0) v = old[(size_t)(keep + ii) * width + c];
+                acc = fmaf(a.taps_w[(size_t)c * a.taps + j], v, acc);
+            }
+            acc = fmaf(a.taps_w[(size_t)c * a.taps + keep], cur, acc);
+            hm[(size_t)r * width + c] = from_float<OutT>(cur + acc);
+            if (s_new >= 0) fresh[(size_t)s_new * width + c] = cur;
+        }
+    }
+}
+
+// x float32 [*, width]; w float32 [width]; h (and hm, with a filter) [rows, width] of `out_dtype`; taps_w float32 [width, taps]
+// or null (taps 1); state float32 [slots, slot_floats]; the step's row ranges, histories and slots as a step gives them;
+// zero: a float buffer of zero_count values (a multiple of 4, 16-byte aligned) cleared in passing, or null.
+LLMX_EXPORT int llmx_group_norm_conv(const float* x, const float* w, int width, int groups, float eps, const int* row_index,
+                                     int rows, void* h, void* hm, int out_dtype, const float* taps_w, int taps, float* state,
+                                     long long slot_floats, long long state_off, const int* row_request, const int* row_start,
+                                     const int* row_count, const int* history, const int* slot_in, const int* slot_out,
+                                     int requests, float* zero, long long zero_count, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0 || groups <= 0 || width % groups || taps < 1 || taps * groups > 8192) return LLMX_ERR_BAD_ARGUMENT;
+    if (zero && (zero_count % 4 || ((uintptr_t)zero & 15))) return LLMX_ERR_BAD_ARGUMENT;
+    if (taps > 1 && (taps_w == nullptr || hm == nullptr || state == nullptr || row_index != nullptr || row_request == nullptr ||
+                     state_off + (long long)(taps - 1) * width > slot_floats))
+        return LLMX_ERR_BAD_ARGUMENT;
+    GroupNormConv a{x, w, width, groups, eps, row_index, rows, taps_w, taps, state, slot_floats, state_off, row_request, row_start,
+                    row_count, history, slot_in, slot_out, requests, zero, zero_count};
+    long long zero_blocks = zero ? (zero_count / 4 + 4 * 256 - 1) / (4 * 256) : 0;
+    zero_blocks = zero_blocks > 1024 ? 1024 : zero_blocks;
+    const dim3 grid((unsigned)(rows + (taps > 1 ? requests : 0) + zero_blocks));
+    const size_t smem = (size_t)taps * groups * sizeof(float);
+    if (out_dtype == LLMX_BF16)
+        launch_kernel(group_norm_conv_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, a, (__nv_bfloat16*)h, (__nv_bfloat16*)hm);
+    else if (out_dtype == LLMX_F32)
+        launch_kernel(group_norm_conv_kernel<float>, grid, dim3(256), smem, stream, a, (float*)h, (float*)hm);
+    else
+        return LLMX_ERR_UNSUPPORTED;
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Token embedding times a factor, plus a row of a second table chosen by the pair (token before, token):
+//   x[r] = table[id] * scale + pair_table[(before * mul_prev + id * mul_cur) mod buckets]
+// and row `buckets` of the pair table for a request's first token.  The token before a step's first row is the
+// request's state (one int32 in its slot); the step's last token goes to the slot the step writes (blocks beyond the rows,
+// one a request).
+template <typename T>
+__global__ void embed_pairs_kernel(const T* __restrict__ table, const T* __restrict__ pair_table, const int* __restrict__ ids,
+                                   float* __restrict__ x, int rows, int width, int vocab, float scale, int buckets,
+                                   long long mul_prev, long long mul_cur, const int* __restrict__ row_request,
+                                   const int* __restrict__ row_start, const int* __restrict__ row_count,
+                                   const int* __restrict__ history, int* __restrict__ state, long long slot_ints,
+                                   const int* __restrict__ slot_in, const int* __restrict__ slot_out) {
+    pdl_trigger();
+    pdl_wait();
+    if ((int)blockIdx.x >= rows) {
+        const int q = blockIdx.x - rows;
+        const int n = row_count[q];
+        if (threadIdx.x == 0 && n > 0) state[(size_t)slot_out[q] * slot_ints] = ids[row_start[q] + n - 1];
+        return;
+    }
+    const int r = blockIdx.x;
+    const int q = row_request[r];
+    const int i0 = r - row_start[q];
+    int id = ids[r];
+    id = id < 0 ? 0 : id >= vocab ? vocab - 1 : id;
+    int before = -1;
+    if (i0 > 0) before = ids[r - 1];
+    else if (history[q] > 0) before = state[(size_t)slot_in[q] * slot_ints];
+    const long long pair = before < 0 ? (long long)buckets : ((long long)before * mul_prev + (long long)id * mul_cur) % (long long)buckets;
+    const T* src = table + (size_t)id * width;
+    const T* psrc = pair_table + (size_t)pair * width;
+    float* dst = x + (size_t)r * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = fmaf(to_float(src[c]), scale, to_float(psrc[c]));
+}
+
+LLMX_EXPORT int llmx_embed_pairs(const void* table, const void* pair_table, int table_dtype, const int* ids, float* x, int rows,
+                                 int width, int vocab, float scale, int buckets, long long mul_prev, long long mul_cur,
+                                 const int* row_request, const int* row_start, const int* row_count, const int* history,
+                                 int* state, long long slot_ints, const int* slot_in, const int* slot_out, int requests,
+                                 cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (buckets <= 0 || width <= 0 || vocab <= 0 || state == nullptr || slot_ints <= 0) return LLMX_ERR_BAD_ARGUMENT;
+    const dim3 grid(rows + requests);
+    if (table_dtype == LLMX_BF16)
+        launch_kernel(embed_pairs_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pair_table,
+                      ids, x, rows, width, vocab, scale, buckets, mul_prev, mul_cur, row_request, row_start, row_count, history, state,
+                      slot_ints, slot_in, slot_out);
+    else if (table_dtype == LLMX_F32)
+        launch_kernel(embed_pairs_kernel<float>, grid, dim3(256), 0, stream, (const float*)table, (const float*)pair_table, ids, x, rows,
+                      width, vocab, scale, buckets, mul_prev, mul_cur, row_request, row_start, row_count, history, state, slot_ints,
+                      slot_in, slot_out);
+    else
+        return LLMX_ERR_UNSUPPORTED;
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// x[r, c] += factor * row_factor[r] * y[r, c]   (row_factor null: 1), float32.
+__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ row_factor,
+                                float factor, int width, long long total) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float f = row_factor ? factor * row_factor[i / width] : factor;
+    x[i] = fmaf(f, y[i], x[i]);
+}
+
+LLMX_EXPORT int llmx_add_rows(float* x, const float* y, const float* row_factor, float factor, int rows, int width,
+                              cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const long long total = (long long)rows * width;
+    launch_kernel(add_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, y, row_factor, factor, width, total);
+    return launch_status();
+}
+
+// x <- cap * tanh(x / cap), float32.
+__global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+LLMX_EXPORT int llmx_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.0f)) return LLMX_ERR_BAD_ARGUMENT;
+    launch_kernel(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, cap);
+    return launch_status();
+}

@@ -9,7 +9,9 @@ first step that names it.  A mixer made of several (two side by side) needs
 several entries: its `cache_spec()` is a tuple, and the step names as many entries.
 A step may also ask for the embedding output (the stream as it was before the
 first layer) to be added to the stream before its block runs (`add_embedding`),
-for a model that runs a stretch of layers several times.
+for a model that runs a stretch of layers several times.  An embedding that keeps something per request (the
+token before a step's rows) says so through `cache_spec()`; the model then names one more cache entry for it
+(`embedding_entry`) and hands it the step.
 
 `Model` knows no architecture.  An architecture's builder
 (`llmx_b200/models/qwen3.py`) constructs the parts from its configuration and
@@ -94,7 +96,7 @@ class Model:
                  block_prefix: Callable[[int], str] = lambda i: f"model.layers.{i}.",
                  embedding_prefix: str = "model.embed_tokens.", head_norm_prefix: str = "model.norm.",
                  head_prefix: str = "lm_head.", vocab_size: int, max_positions: int,
-                 ignorable: Iterable[str] = (), eos_ids: Sequence[int] = ()):
+                 ignorable: Iterable[str] = (), eos_ids: Sequence[int] = (), embedding_entry: Optional[int] = None):
         self.embedding, self.blocks, self.head = embedding, list(blocks), head
         self.order: List[LayerStep] = list(order) if order is not None else [
             LayerStep(i, i) for i in range(len(self.blocks))]
@@ -103,6 +105,10 @@ class Model:
         self.vocab_size, self.max_positions = int(vocab_size), int(max_positions)
         self.ignorable: Set[str] = set(ignorable)
         self.eos_ids = tuple(eos_ids)
+        self.embedding_entry = embedding_entry
+        needs = getattr(embedding, "cache_spec", lambda: None)()
+        if (needs is None) != (embedding_entry is None):
+            raise ValueError("the embedding's cache entry is named exactly when the embedding keeps something per request")
         self.precision: Optional[Precision] = None
         self._native: Optional[NativeHandle] = None
         self._native_tried = False
@@ -111,6 +117,9 @@ class Model:
     def _check_order(self) -> None:
         writers: Dict[int, int] = {}
         named = set()
+        if self.embedding_entry is not None:
+            named.add(self.embedding_entry)
+            writers[self.embedding_entry] = -1
         for n, s in enumerate(self.order):
             if not 0 <= s.block < len(self.blocks):
                 raise ValueError(f"layer order step {n} names block {s.block}, the model has {len(self.blocks)}")
@@ -140,6 +149,8 @@ class Model:
     # -- what the cache manager needs ------------------------------------------
     def cache_entry_specs(self) -> list:
         specs: Dict[int, object] = {}
+        if self.embedding_entry is not None:
+            specs[self.embedding_entry] = self.embedding.cache_spec()
         for s in self.order:
             for e, spec in zip(_as_tuple(s.cache_entry), _as_tuple(self.blocks[s.block].cache_spec())):
                 if e in specs and specs[e] != spec:
@@ -259,7 +270,10 @@ class Model:
             logits = torch.empty((wanted, self.vocab_size), dtype=torch.float32, device=step.token_ids.device) if wanted else None
             runtime.check(rt.llmx_model_forward(self.native, ctypes.byref(s), runtime.ptr(logits)), "forward")
             return logits
-        x = self.embedding.forward(step.token_ids)
+        if self.embedding_entry is not None:
+            x = self.embedding.forward_step(step, self.embedding_entry)
+        else:
+            x = self.embedding.forward(step.token_ids)
         x0 = None
         if any(s.add_embedding for s in self.order):
             x0 = x.clone()

@@ -111,14 +111,24 @@ _SIGNATURES = {
                                           _p, ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _i, _i, _p],
     ("attention_split", "llmx_qk_norm_rope_write"): [_p, _i, _p, _p, _f, _p, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _p],
     ("attention_split", "llmx_qkv_finish"): [_p, _i, _p, _p, _i, _p, ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p, _p, _p, _p, _i,
-                                             _f, _p, _i, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p],
-    ("attention_split", "llmx_attention_split"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p, _p],
+                                             _f, _p, _i, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _p],
+    ("attention_split", "llmx_attention_split"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p,
+                                                  _f, _p, _i, _p, _i, _p],
     ("attention_split", "llmx_attention_tiled_fits"): [_i, _i, _i, _i],
-    ("attention_split", "llmx_attention_tiled"): [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p],
+    ("attention_split", "llmx_attention_tiled"): [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f,
+                                                  _f, _p, _i, _p, _i, _p],
     ("moe", "llmx_moe_route"): [_p, _p, _i, _i, _i, _i, _p, _p, _p, _i, _p],
     ("moe", "llmx_moe_product_few"): [_p, _i, _p, _p, _p, _i, _i, _i, _i, _p, _i, _i, _i, _i, _p],
     ("moe", "llmx_moe_product"): [_p, _i, _p, _i, _p, _p, _p, _i, _i, _p, _i, _i, _i, _i, _i, _p],
     ("moe", "llmx_moe_combine"): [_p, _p, _i, _i, _i, _f, _p],
+    ("moe", "llmx_moe_router"): [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p, _p, _p],
+    ("moe", "llmx_moe_combine_weighted"): [_p, _p, _p, _i, _i, _i, _f, _p],
+    ("rowwise", "llmx_group_norm_conv"): [_p, _p, _i, _i, _f, _p, _i, _p, _p, _i, _p, _i, _p, ctypes.c_longlong, ctypes.c_longlong,
+                                          _p, _p, _p, _p, _p, _p, _i, _p, ctypes.c_longlong, _p],
+    ("rowwise", "llmx_embed_pairs"): [_p, _p, _i, _p, _p, _i, _i, _i, _f, _i, ctypes.c_longlong, ctypes.c_longlong, _p, _p, _p, _p, _p,
+                                      ctypes.c_longlong, _p, _p, _i, _p],
+    ("rowwise", "llmx_add_rows"): [_p, _p, _p, _f, _i, _i, _p],
+    ("rowwise", "llmx_softcap"): [_p, ctypes.c_longlong, _f, _p],
     ("latent_attention", "llmx_latent_write"): [_p, _i, _i, _p, _p, _i, _p, _f, _p, _i, _i, _f, _p, _p, _p, _i, _i, _i, _i, _p],
     ("latent_attention", "llmx_latent_attention"): [_p, _i, _p, _i, _p, _p, _i, _p, _p, _i, _i, _f, _p, _p, _p, _i, _i, _i, _i,
                                                     _i, _i, _i, _i, _i, _f, _p],
@@ -458,6 +468,75 @@ def add_(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
 
 # ---------------------------------------------------------------------------
 # Matrix-state recurrences.
+def group_norm_conv(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, out: torch.Tensor,
+                    row_index: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None,
+                    taps_w: Optional[torch.Tensor] = None, filtered: Optional[torch.Tensor] = None,
+                    state: Optional[torch.Tensor] = None, step=None, state_off: int = 0) -> torch.Tensor:
+    """RMS norm in `groups` equal consecutive parts of a row (each part by its own root mean square), times the weight, to
+    `out`; with `taps_w` float32 [width, taps] also `filtered` = out + a causal filter of out over the request's rows (last
+    tap on the row itself, zeros before the request), whose earlier inputs lie in `state` float32 [slots, floats] at
+    `state_off` ([taps - 1][width], read at the request's slot, written at its spare).  `step`: the StepBatch."""
+    _cuda(x, weight, out, row_index, zero, taps_w, filtered, state)
+    rows = x.shape[0] if row_index is None else row_index.numel()
+    width = x.shape[1]
+    _need(x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == width and width % groups == 0,
+          "group_norm: float32 rows and weight, a width the groups divide")
+    _need(tuple(out.shape) == (rows, width), "group_norm: output shape does not fit")
+    _need(row_index is None or row_index.dtype == torch.int32, "group_norm: row_index must be int32")
+    _need(zero is None or (zero.dtype == torch.float32 and zero.numel() % 4 == 0 and zero.data_ptr() % 16 == 0), "group_norm: zero buffer float32, 16-byte pieces")
+    taps = 1
+    if taps_w is not None:
+        taps = taps_w.shape[1]
+        _need(taps_w.dtype == torch.float32 and tuple(taps_w.shape) == (width, taps), "group_norm: taps float32 [width, taps]")
+    if taps > 1:
+        _need(filtered is not None and filtered.dtype == out.dtype and tuple(filtered.shape) == (rows, width) and row_index is None
+              and step is not None and rows == step.rows, "group_norm: the filter wants a second output and the step")
+        _need(state is not None and state.dtype == torch.float32 and state.dim() == 2 and state_off + (taps - 1) * width <= state.shape[1],
+              "group_norm: state slots too small for the filter's inputs")
+    s = step if taps > 1 else None
+    _check(_fn("rowwise", "llmx_group_norm_conv")(
+        _ptr(x), _ptr(weight), width, int(groups), float(eps), _ptr(row_index), rows, _ptr(out), _ptr(filtered if taps > 1 else None),
+        _code(out), _ptr(taps_w if taps > 1 else None), taps, _ptr(state if taps > 1 else None), 0 if s is None else state.shape[1],
+        int(state_off), _ptr(s.row_request if s else None), _ptr(s.row_start if s else None), _ptr(s.row_count if s else None),
+        _ptr(s.history if s else None), _ptr(s.state_slots if s else None), _ptr(s.state_slots_out if s else None),
+        s.requests if s else 0, _ptr(zero), 0 if zero is None else zero.numel(), _stream()), "group_norm_conv")
+    return out
+
+
+def embed_pairs(table: torch.Tensor, pair_table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float, buckets: int,
+                mul_prev: int, mul_cur: int, state: torch.Tensor, step) -> torch.Tensor:
+    """out[r] = table[id] * scale + pair_table[(id before * mul_prev + id * mul_cur) mod buckets], row `buckets` of the pair
+    table for a request's first token; the id before a step's first row is read from `state` int32 [slots, 1] at the
+    request's slot, and the step's last id goes to its spare."""
+    _cuda(table, pair_table, ids, out, state)
+    rows, width = ids.numel(), table.shape[1]
+    _need(table.dtype == pair_table.dtype and pair_table.shape[1] == width and pair_table.shape[0] == buckets + 1, "embed_pairs: tables do not fit")
+    _need(ids.dtype == torch.int32 and out.dtype == torch.float32 and tuple(out.shape) == (rows, width) and rows == step.rows, "embed_pairs: ids int32, out float32 [rows, width]")
+    _need(state.dtype == torch.int32 and state.dim() == 2, "embed_pairs: state int32 [slots, ints]")
+    _check(_fn("rowwise", "llmx_embed_pairs")(
+        _ptr(table), _ptr(pair_table), _code(table), _ptr(ids), _ptr(out), rows, width, table.shape[0], float(scale), int(buckets),
+        int(mul_prev), int(mul_cur), _ptr(step.row_request), _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history),
+        _ptr(state), state.shape[1], _ptr(step.state_slots), _ptr(step.state_slots_out), step.requests, _stream()), "embed_pairs")
+    return out
+
+
+def add_rows_(x: torch.Tensor, y: torch.Tensor, factor: float = 1.0, row_factor: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x[r] += factor * row_factor[r] * y[r] (row_factor None: 1); float32 rows."""
+    _cuda(x, y, row_factor)
+    _need(x.dtype == torch.float32 and y.dtype == torch.float32 and x.shape == y.shape and x.dim() == 2, "add_rows: float32 rows of one shape")
+    _need(row_factor is None or (row_factor.dtype == torch.float32 and row_factor.numel() == x.shape[0]), "add_rows: a float32 factor per row")
+    _check(_fn("rowwise", "llmx_add_rows")(_ptr(x), _ptr(y), _ptr(row_factor), float(factor), x.shape[0], x.shape[1], _stream()), "add_rows")
+    return x
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap), float32, in place."""
+    _cuda(x)
+    _need(x.dtype == torch.float32 and cap > 0, "softcap: float32 values, a positive cap")
+    _check(_fn("rowwise", "llmx_softcap")(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+    return x
+
+
 def _strided_rows(t: torch.Tensor, what: str) -> int:
     _need(t.is_cuda and t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1, f"{what}: float32 rows, contiguous within a row")
     return t.stride(0) if t.shape[0] > 1 else t.shape[1]
@@ -576,7 +655,8 @@ def qkv_finish(proj: torch.Tensor, heads: int, kv_heads: int, key_dim: int, valu
                cache: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
                taps_w: Optional[torch.Tensor] = None, state: Optional[torch.Tensor] = None, conv_off: int = 0,
                norm: str = "none", q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
-               freq: Optional[torch.Tensor] = None, neighbours: bool = False) -> None:
+               freq: Optional[torch.Tensor] = None, neighbours: bool = False, rot_mag: float = 1.0,
+               vfreq: Optional[torch.Tensor] = None) -> None:
     """The general finishing of a stacked q/k/v product's rows (csrc/attention_split.cu, `QkvFinish`): proj float32 [rows, q
     (heads * D) | k (kv_heads * D) | v (kv_heads * V)] (a view whose rows may be strided; kv_heads 0: queries alone) plus
     `bias` [channels]; a causal filter `taps_w` [channels, taps] per channel whose earlier inputs lie in `state`
@@ -584,16 +664,21 @@ def qkv_finish(proj: torch.Tensor, heads: int, kv_heads: int, key_dim: int, valu
     per q and k head `norm` = "none" | "before" | "after" the rotation, with weights [D] or without; a rotation of the
     first 2 * len(freq) values of a head by position * freq[i], pairs (i, i + len(freq)) or `neighbours` (2i, 2i + 1);
     queries to q_out [rows, heads * D], [k ; v] to cache [pages, 1, kv_heads, page, D + V] at `slots`, or, where the cache
-    has planes of keys and of values, [pages, 2, kv_heads, page, D] (D = V), to those.  `step`: the StepBatch."""
-    _cuda(bias, taps_w, state, q_weight, k_weight, freq, slots, q_out, cache)
+    has planes of keys and of values, [pages, 2, kv_heads, page, D] (D = V), to those.  `step`: the StepBatch.
+    `norm` "whole": one RMS norm over all of a row's queries and one over all of its keys, before they are split into
+    heads, with weights [heads * D] and [kv_heads * D].  `rot_mag`: a factor on the rotation's cosines and sines.  `vfreq`
+    float32 [V / 2]: the values are rotated too, over all of V, pair m by position * vfreq[m], in the same pairing."""
+    _cuda(bias, taps_w, state, q_weight, k_weight, freq, slots, q_out, cache, vfreq)
     rows = proj.shape[0]
     channels = (heads + kv_heads) * key_dim + kv_heads * value_dim
     _need(proj.is_cuda and proj.dtype == torch.float32 and proj.dim() == 2 and proj.shape[1] == channels and proj.stride(1) == 1,
           "qkv_finish: product rows float32 [rows, q | k | v]")
     _need(tuple(q_out.shape) == (rows, heads * key_dim) and rows == step.rows, "qkv_finish: q_out shape or the step's rows do not fit")
-    _need(norm in ("none", "before", "after"), "qkv_finish: norm is none, before or after")
-    for t, n in ((bias, channels), (q_weight, key_dim), (k_weight, key_dim)):
-        _need(t is None or (t.dtype == torch.float32 and t.numel() == n), "qkv_finish: float32 bias [channels], norm weights [D]")
+    _need(norm in ("none", "before", "after", "whole"), "qkv_finish: norm is none, before, after or whole")
+    qn, kn = (heads * key_dim, kv_heads * key_dim) if norm == "whole" else (key_dim, key_dim)
+    for t, n in ((bias, channels), (q_weight, qn), (k_weight, kn)):
+        _need(t is None or (t.dtype == torch.float32 and t.numel() == n), "qkv_finish: float32 bias [channels], norm weights [D] (whole: [heads * D])")
+    _need(vfreq is None or (vfreq.dtype == torch.float32 and 2 * vfreq.numel() == value_dim), "qkv_finish: value frequencies float32 [V / 2]")
     taps = 1
     if taps_w is not None:
         taps = taps_w.shape[1]
@@ -611,15 +696,44 @@ def qkv_finish(proj: torch.Tensor, heads: int, kv_heads: int, key_dim: int, valu
         _ptr(proj), proj.stride(0) if rows > 1 else proj.shape[1], _ptr(bias), _ptr(taps_w), taps, _ptr(state),
         0 if state is None else state.shape[1], int(conv_off), _ptr(step.row_request), _ptr(step.row_start), _ptr(step.row_count),
         _ptr(step.history), _ptr(step.state_slots), _ptr(step.state_slots_out), _ptr(q_weight), _ptr(k_weight),
-        ("none", "before", "after").index(norm), float(eps), _ptr(freq), 0 if freq is None else freq.numel(), 1 if neighbours else 0,
+        ("none", "before", "after", "whole").index(norm), float(eps), _ptr(freq), 0 if freq is None else freq.numel(), 1 if neighbours else 0,
         _ptr(step.positions), _ptr(slots), _ptr(q_out), _code(q_out), _ptr(cache), _code(cache) if cache is not None else F32, rows,
         step.requests, heads, kv_heads, key_dim, value_dim, cache.shape[3] if cache is not None else 1,
-        cache.shape[1] if cache is not None else 1, _stream()), "qkv_finish")
+        cache.shape[1] if cache is not None else 1, float(rot_mag), _ptr(vfreq), _stream()), "qkv_finish")
+
+
+class SoftmaxExtras:
+    """What a design may add to the softmax of `attention_split` / `attention_tiled` (csrc/attention_split.cu, `AttnExtras`):
+    `softcap` c > 0: score <- c tanh(score / c) after the scale; `sink`: a float32 tensor [heads] whose exp joins each head's
+    denominator (it has no key and no value), or the string "zero" for a sink of 0 (one is added to the denominator);
+    `vfreq` float32 [V / 2]: the cached values were rotated by their positions, and a row's output is turned back by its
+    own (`v_neighbours`: pairs (2m, 2m + 1) instead of (m, m + V / 2))."""
+
+    def __init__(self, softcap: Optional[float] = None, sink=None, vfreq: Optional[torch.Tensor] = None, v_neighbours: bool = False):
+        self.softcap, self.sink, self.vfreq, self.v_neighbours = softcap, sink, vfreq, bool(v_neighbours)
+
+    def checked(self, heads: int, value_dim: int):
+        learned = isinstance(self.sink, torch.Tensor)
+        if learned:
+            _cuda(self.sink)
+            _need(self.sink.dtype == torch.float32 and self.sink.numel() == heads, "attention: a sink per head, float32")
+        else:
+            _need(self.sink in (None, "zero"), "attention: sink is a tensor [heads], \"zero\" or None")
+        if self.vfreq is not None:
+            _cuda(self.vfreq)
+            _need(self.vfreq.dtype == torch.float32 and 2 * self.vfreq.numel() == value_dim, "attention: value frequencies float32 [V / 2]")
+        _need(self.softcap is None or self.softcap > 0, "attention: the cap on the scores must be positive")
+        return (float(self.softcap or 0.0), _ptr(self.sink if learned else None), 1 if learned else 2 if self.sink == "zero" else 0,
+                _ptr(self.vfreq), 1 if self.v_neighbours else 0)
+
+
+NO_EXTRAS = SoftmaxExtras()
 
 
 def attention_split(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row_request: torch.Tensor,
                     positions: torch.Tensor, block_tables: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
-                    value_dim: int, window: Optional[int], chunk: Optional[int], scale: float, splits: int = 1) -> torch.Tensor:
+                    value_dim: int, window: Optional[int], chunk: Optional[int], scale: float, splits: int = 1,
+                    extras: Optional["SoftmaxExtras"] = None) -> torch.Tensor:
     """Paged softmax attention, one block per (row, head); q [rows, heads * D] and out [rows, heads * V] of one type;
     cache [pages, 1, kv_heads, page, D + V].  A row at position p reads keys max(p - window + 1, floor(p / chunk) * chunk,
     0) .. p.  `splits` > 1: a row's keys are cut into that many ranges, a block each, merged by a second kernel in
@@ -635,10 +749,11 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row
     _need(block_tables.dim() == 2 and row_request.numel() >= rows and positions.numel() >= rows, "attention: metadata shapes do not fit")
     splits = max(1, min(int(splits), 64))
     partial = torch.empty((rows, heads, splits, value_dim + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
+    x = (extras or NO_EXTRAS).checked(heads, value_dim)
     _check(_fn("attention_split", "llmx_attention_split")(
         _ptr(q), _code(q), _ptr(cache), _code(cache), _ptr(out), _ptr(row_request), _ptr(positions), _ptr(block_tables),
         block_tables.shape[1], rows, heads, kv_heads, key_dim, value_dim, cache.shape[3], int(window or 0), int(chunk or 0),
-        float(scale), splits, _ptr(partial), _stream()), "attention_split", 2 if splits > 1 else 1)
+        float(scale), splits, _ptr(partial), *x, _stream()), "attention_split", 2 if splits > 1 else 1)
     return out
 
 
@@ -649,7 +764,8 @@ def attention_tiled_fits(heads: int, kv_heads: int, key_dim: int, value_dim: int
 
 
 def attention_tiled(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, step, block_tables: torch.Tensor, heads: int,
-                    kv_heads: int, key_dim: int, value_dim: int, window: Optional[int], chunk: Optional[int], scale: float) -> torch.Tensor:
+                    kv_heads: int, key_dim: int, value_dim: int, window: Optional[int], chunk: Optional[int], scale: float,
+                    extras: Optional["SoftmaxExtras"] = None) -> torch.Tensor:
     """`attention_split` on the tensor cores (csrc/attention_split.cu): bfloat16 q [rows, heads * D], out [rows, heads * V]
     and cache; 64 rows that share their keys a block, keys in tiles of 64; softmax weights enter the second product
     as sums of three bfloat16 values.  `step`: the StepBatch (row ranges and histories are read on the device)."""
@@ -663,7 +779,7 @@ def attention_tiled(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ste
     _check(_fn("attention_split", "llmx_attention_tiled")(
         _ptr(q), _ptr(cache), _ptr(out), _ptr(step.row_start), _ptr(step.row_count), _ptr(step.history), _ptr(block_tables),
         block_tables.shape[1], rows, step.requests, heads, kv_heads, key_dim, value_dim, cache.shape[3], int(window or 0),
-        int(chunk or 0), float(scale), _stream()), "attention_tiled")
+        int(chunk or 0), float(scale), *(extras or NO_EXTRAS).checked(heads, value_dim), _stream()), "attention_tiled")
     return out
 
 
@@ -690,9 +806,12 @@ def moe_product_few(a: torch.Tensor, a_div: int, w: torch.Tensor, token_ids: tor
     experts, wn, K = w.shape
     N = wn // 2 if gated else wn
     vocab, top = table.shape
+    # No ids: the table has a row for each row of the step (a router wrote it).
     _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and a.shape[1] == K and a.shape[0] * a_div >= pairs,
           "moe_product_few: bfloat16 rows that fit the weights")
-    _need(token_ids.dtype == torch.int32 and table.dtype == torch.int32 and token_ids.numel() * top >= pairs, "moe_product_few: int32 ids and table")
+    _need(table.dtype == torch.int32 and (vocab * top >= pairs if token_ids is None else
+                                          token_ids.dtype == torch.int32 and token_ids.numel() * top >= pairs),
+          "moe_product_few: int32 ids and table")
     _need(tuple(out.shape) == (pairs, N), "moe_product_few: output shape does not fit")
     _check(_fn("moe", "llmx_moe_product_few")(_ptr(a), int(a_div), _ptr(w), _ptr(token_ids), _ptr(table), top, vocab, pairs, experts,
                                               _ptr(out), _code(out), N, K, 1 if gated else 0, _stream()), "moe_product_few")
@@ -705,9 +824,10 @@ def moe_route(token_ids: torch.Tensor, table: torch.Tensor, experts: int, lists:
     order), counts int32 [experts], tiles int32 [moe_tiles_len] (their number, their size, then (expert, first place) of
     every tile).  `tensor_cores`: the form of `moe_product` that will run (it sets the tiles' size: 128 pairs, else 32)."""
     _cuda(token_ids, table, lists, counts, tiles)
-    rows, (vocab, top) = token_ids.numel(), table.shape
+    vocab, top = table.shape
+    rows = vocab if token_ids is None else token_ids.numel()      # no ids: the table has a row for each row of the step
     for t in (token_ids, table, lists, counts, tiles):
-        _need(t.dtype == torch.int32, "moe_route: int32 tensors")
+        _need(t is None or t.dtype == torch.int32, "moe_route: int32 tensors")
     _need(lists.numel() >= experts * rows * top and counts.numel() >= experts and tiles.numel() >= moe_tiles_len(rows * top, experts),
           "moe_route: outputs too small")
     tile_rows = _moe_tile_rows.get(bool(tensor_cores))
@@ -733,6 +853,34 @@ def moe_product(a: torch.Tensor, a_div: int, w: torch.Tensor, lists: torch.Tenso
                                           experts, _ptr(out), _code(out), N, K, 1 if gated else 0, 1 if tensor_cores else 0,
                                           _stream()), "moe_product")
     return out
+
+
+def moe_router(h: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], experts: int, top: int, choice: torch.Tensor,
+               weight: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
+    """A router on the device: logits h w[:experts]^T + bias in 32-bit (w float32 [experts + extra, K]), the `top` largest to
+    choice int32 [rows, top] (the lower index first among equals), the softmax over the chosen logits to weight float32
+    [rows, top]; the `extra` rows of w after the experts' give gate float32 [rows, extra] through a sigmoid."""
+    _cuda(h, w, bias, choice, weight, gate)
+    rows, K = h.shape
+    extra = w.shape[0] - experts
+    _need(w.dtype == torch.float32 and w.dim() == 2 and w.shape[1] == K and extra >= 0, "moe_router: float32 weights [experts + extra, K]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == experts), "moe_router: float32 bias [experts]")
+    _need(choice.dtype == torch.int32 and tuple(choice.shape) == (rows, top) and weight.dtype == torch.float32
+          and tuple(weight.shape) == (rows, top), "moe_router: choice int32 and weight float32 [rows, top]")
+    _need(extra == 0 or (gate is not None and gate.dtype == torch.float32 and gate.numel() == rows * extra), "moe_router: gate float32 [rows, extra]")
+    _check(_fn("moe", "llmx_moe_router")(_ptr(h), _code(h), _ptr(w), _ptr(bias), rows, K, experts, top, extra, _ptr(choice), _ptr(weight),
+                                         _ptr(gate), _stream()), "moe_router")
+
+
+def moe_combine_weighted_(x: torch.Tensor, y: torch.Tensor, pair_weight: torch.Tensor, top: int, factor: float = 1.0) -> torch.Tensor:
+    """x[row] += factor * sum_k pair_weight[row, k] * y[row * top + k], k in increasing order; float32."""
+    _cuda(x, y, pair_weight)
+    rows, width = x.shape
+    _need(x.dtype == torch.float32 and y.dtype == torch.float32 and tuple(y.shape) == (rows * top, width)
+          and pair_weight.dtype == torch.float32 and pair_weight.numel() == rows * top, "moe_combine: shapes do not fit")
+    _check(_fn("moe", "llmx_moe_combine_weighted")(_ptr(y), _ptr(x), _ptr(pair_weight), rows, top, width, float(factor), _stream()),
+           "moe_combine_weighted")
+    return x
 
 
 def moe_combine_(x: torch.Tensor, y: torch.Tensor, top: int, weight: float) -> torch.Tensor:

@@ -103,7 +103,10 @@ class PartPlan:
 def tensor_name(prefix: str, role: str) -> str:
     """The name of a part's tensor: the part's prefix and the tensor's role.  A part with one tensor may give it the
     empty role; the tensor is then named by the prefix alone, without its trailing dot ("final.norm", not
-    "final.norm.weight")."""
+    "final.norm.weight").  A role that begins with "/" names the tensor by itself, whatever the part's prefix (a second
+    table of an embedding that the files keep at the top level)."""
+    if role.startswith("/"):
+        return role[1:]
     return prefix + role if role else prefix.rstrip(".")
 
 

@@ -77,22 +77,60 @@ class PreNormBlock(Part):
         self.ffn.forward(h, step, x)
 
 
-class ParallelBlock(Part):
-    """x += mixer(norm(x)) + ffn(norm(x)): one norm, and both parts read its output and add into the float32
-    residual.  `ffn` may be None (a layer with a mixer only).  `names`: the prefixes of the three parts' tensors."""
+class InputFilter(Part):
+    """The taps of a short causal filter over time on every channel of a mixer's input, [width, taps] (the last tap lies on
+    the row itself); the block that holds it applies it (`ParallelBlock(input_filter=)`) and keeps its state."""
 
-    def __init__(self, norm: Part, mixer: Part, ffn: Optional[Part], names=("norm", "mixer", "mlp")):
+    def __init__(self, width: int, taps: int, role: str = ""):
+        if taps < 2:
+            raise ValueError("input filter: at least two taps (one tap is no filter)")
+        self.width, self.taps, self.role = int(width), int(taps), role
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self):
+        from ..weights.spec import TensorSpec
+        return {self.role: TensorSpec((self.width, self.taps), std=0.3)}
+
+    def load(self, tensors, precision) -> None:
+        super().load(tensors, precision)
+        self.weight = tensors[self.role].to(torch.float32).contiguous()
+
+
+class ParallelBlock(Part):
+    """x += factor * (mixer(norm(x)) + ffn(norm(x))): one norm, and both parts read its output.  `ffn` may be None (a layer
+    with a mixer only).  `names`: the prefixes of the parts' tensors (norm, mixer, feed-forward, input filter).
+
+    With `factor` 1 and no filter both parts add straight into the float32 residual.  Otherwise their outputs are
+    gathered in a float32 buffer that the norm's launch clears in passing, and one kernel adds `factor` times the buffer
+    into the stream.  `input_filter`: the mixer reads h + filter(h) instead of h = norm(x), a causal filter over the
+    request's rows on each channel (the feed-forward reads h as it is); the norm must offer `forward_filtered`, and the
+    block's cache need is then the mixer's entries and, last, a state entry of (taps - 1) * width floats (the last
+    normed rows of the request)."""
+
+    def __init__(self, norm: Part, mixer: Part, ffn: Optional[Part], names=("norm", "mixer", "mlp", "filter"), factor: float = 1.0,
+                 input_filter: Optional[InputFilter] = None):
         self.norm, self.mixer, self.ffn = norm, mixer, ffn
         self.names = tuple(names)
+        self.factor, self.input_filter = float(factor), input_filter
+        if input_filter is not None and (len(self.names) < 4 or not hasattr(norm, "forward_filtered")):
+            raise ValueError("parallel block: an input filter needs a name and a norm that can apply it")
+        self.gathered = self.factor != 1.0 or input_filter is not None
 
     def children(self) -> Dict[str, Part]:
         out = {self.names[0]: self.norm, self.names[1]: self.mixer}
         if self.ffn is not None:
             out[self.names[2]] = self.ffn
+        if self.input_filter is not None:
+            out[self.names[3]] = self.input_filter
         return out
 
     def cache_spec(self):
-        return self.mixer.cache_spec()
+        spec = self.mixer.cache_spec()
+        if self.input_filter is None:
+            return spec
+        from ..cache.manager import StateSpec
+        mine = StateSpec(((self.input_filter.taps - 1) * self.input_filter.width,), "float32")
+        return (() if spec is None else tuple(spec) if isinstance(spec, (tuple, list)) else (spec,)) + (mine,)
 
     def forward(self, x: torch.Tensor, step: StepBatch, cache_entry: Optional[int], write_cache: bool = True) -> None:
         """x: the float32 residual stream [rows, hidden], updated in place."""
@@ -105,20 +143,40 @@ class ParallelBlock(Part):
                 n = rows * lin.out_features
                 if lin.adds_pieces(rows) and n % 4 == 0:
                     wanted.append((part, lin, n))
-        flat = torch.empty(sum(n for _, _, n in wanted), dtype=torch.float32, device=x.device) if wanted else None
+        # A part may also ask for cleared scratch of its own (`cleared_scratch(rows)` floats, handed over as `part.scratch`).
+        scratch = [(p, (p.cleared_scratch(rows) + 3) & ~3) for p in (self.mixer, self.ffn) if p is not None and hasattr(p, "cleared_scratch")]
+        gathered = ((rows * x.shape[1] + 3) & ~3) if self.gathered else 0
+        total = gathered + sum(n for _, _, n in wanted) + sum(n for _, n in scratch)
+        flat = torch.empty(total, dtype=torch.float32, device=x.device) if total else None
         # Parts with the older way of asking (`wants_cleared`) get theirs cleared by a call of its own.
         others = [_cleared(p, rows, x.device, step) for p in (self.mixer, self.ffn) if p is not None and not hasattr(p, "stored_products")]
-        h = self.norm.forward(x, zero=flat)
+        filter_entry = None
+        if self.input_filter is not None:
+            entries = tuple(cache_entry) if isinstance(cache_entry, (tuple, list)) else (cache_entry,)
+            writes = tuple(write_cache) if isinstance(write_cache, (tuple, list)) else (write_cache,) * len(entries)
+            filter_entry, entries, writes = entries[-1], entries[:-1], writes[:-1]
+            cache_entry = None if not entries else entries[0] if len(entries) == 1 else entries
+            write_cache = True if not writes else writes[0] if len(writes) == 1 else writes
+            h, hm = self.norm.forward_filtered(x, self.input_filter.weight, step.state(filter_entry), step, zero=flat)
+        else:
+            h = hm = self.norm.forward(x, zero=flat)
         for z in others:
             if z is not None:
                 z.zero_()
-        at = 0
+        at = gathered
         for part, lin, n in wanted:
             part.cleared_outputs[id(lin)] = flat[at:at + n].view(rows, lin.out_features)
             at += n
-        self.mixer.forward(h, step, cache_entry, x, write_cache)
+        for part, n in scratch:
+            part.scratch = flat[at:at + n]
+            at += n
+        out = flat[:rows * x.shape[1]].view(rows, x.shape[1]) if self.gathered else x
+        self.mixer.forward(hm, step, cache_entry, out, write_cache)
         if self.ffn is not None:
-            self.ffn.forward(h, step, x)
+            self.ffn.forward(h, step, out)
+        if self.gathered:
+            from .. import ops
+            ops.add_rows_(x, out, self.factor)
 
 
 class SandwichBlock(Part):

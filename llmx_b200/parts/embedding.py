@@ -53,6 +53,45 @@ class TokenEmbedding(Part):
         return x
 
 
+class PairHashEmbedding(TokenEmbedding):
+    """x[r] = table[id] * scale + pairs[(id before * mul_prev + id * mul_cur) mod buckets]; a request's first token takes
+    row `buckets` (the last) of the pair table.  The id before a step's first row is the request's state: one int32 in a
+    state slot (`cache_spec`), read at the slot the step reads and written, with the step's last id, at the slot it
+    writes.  `pair_role`: the pair table's tensor role (with a leading "/" a name of its own)."""
+
+    def __init__(self, vocab: int, hidden: int, buckets: int, mul_prev: int, mul_cur: int, scale: float = 1.0, role: str = "weight",
+                 pair_role: str = "pairs"):
+        super().__init__(vocab, hidden, scale, role)
+        self.buckets, self.mul_prev, self.mul_cur, self.pair_role = int(buckets), int(mul_prev), int(mul_cur), pair_role
+        self.pairs: Optional[torch.Tensor] = None
+
+    def cache_spec(self):
+        from ..cache.manager import StateSpec
+        return StateSpec((1,), "int32")
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.role: TensorSpec((self.vocab, self.hidden), "table"),
+                self.pair_role: TensorSpec((self.buckets + 1, self.hidden), "table")}
+
+    def load(self, tensors, precision: Precision) -> None:
+        super().load(tensors, precision)
+        self.pairs = tensors[self.pair_role].to(precision.act).contiguous()
+
+    @property
+    def native(self):
+        return None
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        raise runtime.KernelError("a pair embedding needs the step (the token before a request's rows): forward_step")
+
+    def forward_step(self, step: StepBatch, cache_entry: int) -> torch.Tensor:
+        from .. import ops
+        ids = step.token_ids
+        x = torch.empty((ids.numel(), self.hidden), dtype=torch.float32, device=ids.device)
+        return ops.embed_pairs(self.table, self.pairs, ids, x, self.scale, self.buckets, self.mul_prev, self.mul_cur,
+                               step.state(cache_entry), step)
+
+
 class LogitsHead(Part):
     """Logits for the rows that want them: gather, norm, product (src/model/arch/blocks.hpp:267-272).
 
@@ -61,10 +100,12 @@ class LogitsHead(Part):
     """
 
     def __init__(self, norm: Part, vocab: int, hidden: int, tied_to: Optional[TokenEmbedding] = None, scale: float = 1.0,
-                 role: str = "weight"):
-        """`scale`: a factor on the logits (applied to the float32 product); `role`: the weight's tensor role."""
+                 role: str = "weight", softcap: Optional[float] = None):
+        """`scale`: a factor on the logits (applied to the float32 product); `role`: the weight's tensor role; `softcap` c:
+        logits <- c tanh(logits / c), last."""
         self.norm, self.vocab, self.hidden, self.tied_to = norm, int(vocab), int(hidden), tied_to
         self.scale, self.role = float(scale), role
+        self.softcap = float(softcap) if softcap else None
         self.linear: Optional[Linear] = None
         self._native: Optional[NativeHandle] = None
         self._native_tried = False
@@ -88,7 +129,7 @@ class LogitsHead(Part):
     def native(self):
         if not self._native_tried:
             self._native_tried = True
-            norm = self.norm.native if self.scale == 1.0 else None
+            norm = self.norm.native if self.scale == 1.0 and self.softcap is None else None
             if norm:
                 d = self.linear.desc()
                 self._native = NativeHandle(runtime.lib().llmx_head_create(norm, ctypes.byref(d)), keep=(self.norm, self.linear.weight))
@@ -102,4 +143,7 @@ class LogitsHead(Part):
         if self.scale != 1.0:
             from .. import ops
             ops.scale_(logits, self.scale)
+        if self.softcap is not None:
+            from .. import ops
+            ops.softcap_(logits, self.softcap)
         return logits

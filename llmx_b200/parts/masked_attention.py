@@ -29,6 +29,16 @@ Options for designs that vary it (any of them makes the rows go through the gene
     shared_kv True        the mixer has no key and value tensors: it reads the cache entry another layer's mixer of the
                           same geometry wrote (the layer order names that entry and does not write it), with queries,
                           filter state and everything else of its own
+    output_bias False     with `bias`, the output product has none (biases on q, k and v alone)
+    qk_norm "whole"       one RMS norm over all of a row's queries and one over all of its keys, before they are split into
+                          heads and rotated, with weights of heads * D and kv_heads * D values
+    rot_freq, rot_magnitude   the rotation's frequencies [rot_dims / 2] as the design scales them (float64 or float32, rounded
+                          once to 32-bit; default base^(-2i / rot_dims) / rot_factor) and a factor on cosines and sines
+    softcap c             score <- c tanh(score / c), after the scale
+    sink "learned" | "zero"   exp(sink_h) joins head h's softmax denominator, a learned number per head (role "sink") that has
+                          no key and no value; "zero": a sink of 0 (one is added to the denominator)
+    rotate_values True    the value of position j is rotated by j over all of V (pair m by j * rot_base^(-2m / V), no scaling,
+                          in the q/k pairing) and cached so; a row's output is turned back by its own position
 With a filter the mixer's cache need is a pair (keys and values, filter state) and `forward` is handed a pair of entries.
 
     rounded_weights True  the design lets softmax weights enter the product with the values rounded to bfloat16 (the
@@ -59,7 +69,9 @@ class MaskedAttention(Part):
                  qk_norm_eps: Optional[float] = None, rot_dims: int = 0, rot_base: float = 10000.0, rot_factor: float = 1.0,
                  window: Optional[int] = None, chunk: Optional[int] = None,
                  names=("q", "k", "v", "o", "q.norm", "k.norm"), bias: bool = False, taps: int = 1, pairing: str = "halves",
-                 qk_norm: str = "before", qk_norm_weight: bool = True, shared_kv: bool = False, rounded_weights: bool = False):
+                 qk_norm: str = "before", qk_norm_weight: bool = True, shared_kv: bool = False, rounded_weights: bool = False,
+                 output_bias: Optional[bool] = None, rot_freq=None, rot_magnitude: float = 1.0, softcap: Optional[float] = None,
+                 sink: Optional[str] = None, rotate_values: bool = False, sink_role: str = "sink"):
         if heads % kv_heads:
             raise ValueError("attention: head count must be divisible by the key/value head count")
         if rot_dims % 2 or rot_dims > key_dim or rot_dims < 0:
@@ -72,15 +84,27 @@ class MaskedAttention(Part):
         self.window, self.chunk, self.names = window, chunk, tuple(names)
         self.q_width, self.k_width, self.v_width = self.heads * self.key_dim, self.kv_heads * self.key_dim, self.kv_heads * self.value_dim
         self.o_width = self.heads * self.value_dim
-        if pairing not in ("halves", "neighbours") or qk_norm not in ("before", "after") or taps < 1:
-            raise ValueError("attention: pairing is halves or neighbours, qk_norm before or after, the filter has at least one tap")
+        if pairing not in ("halves", "neighbours") or qk_norm not in ("before", "after", "whole") or taps < 1:
+            raise ValueError("attention: pairing is halves or neighbours, qk_norm before, after or whole, the filter has at least one tap")
+        if sink not in (None, "learned", "zero") or (softcap is not None and not softcap > 0):
+            raise ValueError("attention: sink is learned, zero or None; a cap on the scores is positive")
+        if rotate_values and self.value_dim % 2:
+            raise ValueError("attention: rotated values need an even value width")
+        if rot_freq is not None and len(rot_freq) != rot_dims // 2:
+            raise ValueError("attention: one frequency for each rotated pair")
+        self.has_output_bias = bool(bias) if output_bias is None else bool(output_bias) and bool(bias)
+        self.rot_freq = None if rot_freq is None else np.asarray(rot_freq, dtype=np.float64)
+        self.rot_magnitude, self.softcap, self.sink, self.sink_role = float(rot_magnitude), softcap, sink, sink_role
+        self.rotate_values = bool(rotate_values)
         self.bias, self.taps, self.pairing, self.qk_norm = bool(bias), int(taps), pairing, qk_norm
         self.qk_norm_weight, self.shared_kv = bool(qk_norm_weight), bool(shared_kv)
-        self.general = self.bias or self.taps > 1 or pairing != "halves" or qk_norm != "before" or not self.qk_norm_weight or self.shared_kv
+        self.general = (self.bias or self.taps > 1 or pairing != "halves" or qk_norm != "before" or not self.qk_norm_weight or self.shared_kv
+                        or self.rot_magnitude != 1.0 or self.rotate_values)
+        plain_softmax = softcap is None and sink is None and not self.rotate_values
         self.channels = self.q_width + (0 if self.shared_kv else self.k_width + self.v_width)
         # Whether the paged kernels can serve this geometry (decided for good in `load`, which knows the path's type).
         self.paged_shape = None
-        if rounded_weights and self.key_dim == self.value_dim and self.chunk is None and self.key_dim in (64, 128) and self.heads // self.kv_heads <= 16:
+        if rounded_weights and plain_softmax and self.key_dim == self.value_dim and self.chunk is None and self.key_dim in (64, 128) and self.heads // self.kv_heads <= 16:
             from .attention import AttentionShape
             self.paged_shape = AttentionShape(self.heads, self.kv_heads, self.key_dim, self.window)
         self.paged = False
@@ -109,16 +133,21 @@ class MaskedAttention(Part):
                 specs[name + ".b"] = TensorSpec((width,), "vector", init="normal", std=0.02)
             if self.taps > 1:
                 specs[name + ".conv"] = TensorSpec((width, self.taps), std=0.3)
-        if self.bias:
+        if self.has_output_bias:
             specs[o + ".b"] = TensorSpec((self.hidden,), "vector", init="normal", std=0.02)
         if self.qk_norm_eps is not None and self.qk_norm_weight:
-            specs[qn] = TensorSpec((self.key_dim,), "vector", init="one_plus_normal", std=0.01)
+            whole = self.qk_norm == "whole"
+            specs[qn] = TensorSpec((self.q_width if whole else self.key_dim,), "vector", init="one_plus_normal", std=0.01)
             if not self.shared_kv:
-                specs[kn] = TensorSpec((self.key_dim,), "vector", init="one_plus_normal", std=0.01)
+                specs[kn] = TensorSpec((self.k_width if whole else self.key_dim,), "vector", init="one_plus_normal", std=0.01)
+        if self.sink == "learned":
+            specs[self.sink_role] = TensorSpec((self.heads,), "vector", init="normal", std=1.0)
         return specs
 
     def frequencies(self) -> np.ndarray:
-        """base^(-2i / rot_dims) / rot_factor, i < rot_dims / 2, rounded once to 32-bit."""
+        """base^(-2i / rot_dims) / rot_factor, i < rot_dims / 2, or the frequencies the design gave, rounded once to 32-bit."""
+        if self.rot_freq is not None:
+            return self.rot_freq.astype(np.float32)
         i = np.arange(self.rot_dims // 2, dtype=np.float64)
         return (np.power(self.rot_base, -2.0 * i / max(self.rot_dims, 1)) / self.rot_factor).astype(np.float32)
 
@@ -134,7 +163,16 @@ class MaskedAttention(Part):
             self.q_norm = tensors[qn].to(torch.float32).contiguous()
             self.k_norm = None if self.shared_kv else tensors[kn].to(torch.float32).contiguous()
         self.in_bias = torch.cat([tensors[n + ".b"] for n in made]).to(torch.float32).contiguous() if self.bias else None
-        self.output_bias = tensors[o + ".b"].to(torch.float32).contiguous() if self.bias else None
+        self.output_bias = tensors[o + ".b"].to(torch.float32).contiguous() if self.has_output_bias else None
+        dev = self.o.weight.device
+        self.vfreq = None
+        if self.rotate_values:
+            m = np.arange(self.value_dim // 2, dtype=np.float64)
+            self.vfreq = torch.from_numpy(np.power(np.float64(self.rot_base), -2.0 * m / self.value_dim).astype(np.float32)).to(dev)
+        sink = tensors[self.sink_role].to(torch.float32).contiguous() if self.sink == "learned" else self.sink
+        self.extras = None
+        if self.softcap is not None or self.sink is not None or self.rotate_values:
+            self.extras = ops.SoftmaxExtras(self.softcap, sink, self.vfreq, self.pairing == "neighbours")
         self.taps_w = torch.cat([tensors[n + ".conv"] for n in made], dim=0).to(torch.float32).contiguous() if self.taps > 1 else None
         self.freq = torch.from_numpy(self.frequencies()).to(self.o.weight.device) if self.rot_dims else None
         self.paged = self.paged_shape is not None and precision.act is torch.bfloat16 and not precision.invariant
@@ -163,7 +201,8 @@ class MaskedAttention(Part):
                            cache=None if self.shared_kv else cache, slots=None if self.shared_kv else slots, bias=self.in_bias,
                            taps_w=self.taps_w, state=step.state(state_entry) if self.taps > 1 else None,
                            norm="none" if self.qk_norm_eps is None else self.qk_norm, q_weight=self.q_norm, k_weight=self.k_norm,
-                           eps=float(self.qk_norm_eps or 0.0), freq=self.freq, neighbours=self.pairing == "neighbours")
+                           eps=float(self.qk_norm_eps or 0.0), freq=self.freq, neighbours=self.pairing == "neighbours",
+                           rot_mag=self.rot_magnitude, vfreq=self.vfreq)
         else:
             ops.qk_norm_rope_write(proj, self.heads, self.kv_heads, self.key_dim, self.value_dim, self.q_norm, self.k_norm,
                                    float(self.qk_norm_eps or 0.0), self.freq, step.positions, slots, q, cache)
@@ -176,13 +215,13 @@ class MaskedAttention(Part):
             ops_attn.paged_attention(q, o, step, cache_entry, self.heads, self.kv_heads, self.key_dim, self.window, self.scale)
         elif self.tiled and step.max_row_count > 4 and cache.dtype is torch.bfloat16:
             ops.attention_tiled(q, cache, o, step, group.block_tables, self.heads, self.kv_heads, self.key_dim, self.value_dim,
-                                self.window, self.chunk, self.scale)
+                                self.window, self.chunk, self.scale, extras=self.extras)
         else:
             span = min(x for x in (step.max_context, self.window, self.chunk) if x)
             blocks = rows * self.heads
             splits = 1 if self.precision.invariant else max(1, min(32, span // 128, 2368 // max(blocks, 1)))
             ops.attention_split(q, cache, o, step.row_request, step.positions, group.block_tables, self.heads, self.kv_heads,
-                                self.key_dim, self.value_dim, self.window, self.chunk, self.scale, splits=splits)
+                                self.key_dim, self.value_dim, self.window, self.chunk, self.scale, splits=splits, extras=self.extras)
         self.o(o, out=residual, accumulate=True)
         if self.output_bias is not None and not self.defer_output_bias:
             ops.add_bias_(residual, self.output_bias)

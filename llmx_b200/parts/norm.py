@@ -65,6 +65,52 @@ class RMSNorm(Part):
         return out
 
 
+class GroupedRMSNorm(Part):
+    """RMS norm in groups: the row is split into `groups` equal consecutive parts, each divided by its own
+    sqrt(mean(part^2) + eps), and the whole is multiplied by the weight; 32-bit arithmetic (csrc/rowwise.cu,
+    `llmx_group_norm_conv`).  The same interface as RMSNorm (one group is the plain RMS norm); it has no twin in the native
+    runtime.  `forward_filtered` also gives the normed rows plus a short causal filter of them over the request's rows
+    (what a block hands to its mixer when the design filters the mixer's input), in the same launch."""
+
+    def __init__(self, width: int, eps: float, groups: int = 1, role: str = "weight"):
+        if groups < 1 or width % groups:
+            raise ValueError("grouped norm: the groups must divide the width")
+        self.width, self.eps, self.groups, self.role = int(width), float(eps), int(groups), role
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.role: TensorSpec((self.width,), "vector", init="one_plus_normal", std=0.01)}
+
+    def load(self, tensors, precision: Precision) -> None:
+        super().load(tensors, precision)
+        self.weight = tensors[self.role].to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                row_index: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+                zero: Optional[torch.Tensor] = None) -> torch.Tensor:
+        from .. import ops
+        rows = x.shape[0] if row_index is None else row_index.numel()
+        if out is None:
+            out = torch.empty((rows, self.width), dtype=out_dtype or self.precision.act, device=x.device)
+        if zero is not None and (zero.numel() % 4 or zero.data_ptr() % 16):
+            zero.zero_()
+            zero = None
+        return ops.group_norm_conv(x, self.weight, self.eps, self.groups, out, row_index=row_index, zero=zero)
+
+    def forward_filtered(self, x: torch.Tensor, taps_w: torch.Tensor, state: torch.Tensor, step, zero: Optional[torch.Tensor] = None,
+                         state_off: int = 0):
+        """(h, h + filter(h)): `taps_w` float32 [width, taps]; the filter's earlier inputs lie in `state` at `state_off`."""
+        from .. import ops
+        rows = x.shape[0]
+        both = torch.empty((2, rows, self.width), dtype=self.precision.act, device=x.device)
+        if zero is not None and (zero.numel() % 4 or zero.data_ptr() % 16):
+            zero.zero_()
+            zero = None
+        ops.group_norm_conv(x, self.weight, self.eps, self.groups, both[0], zero=zero, taps_w=taps_w, filtered=both[1],
+                            state=state, step=step, state_off=state_off)
+        return both[0], both[1]
+
+
 class LayerNorm(Part):
     """y = (x - mean(x)) / sqrt(var(x) + eps) * w (+ b), var the mean of squared deviations; 32-bit arithmetic
     (csrc/rowwise.cu, `llmx_layernorm_affine`).  `role`: the weight's tensor role ("" names it by the part's prefix

@@ -47,6 +47,18 @@ def blended_frequencies(base: float, dims: int, factor: float, original: float, 
     return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
 
 
+def banded_frequencies(base: float, dims: int, factor: float, low: float, high: float, original: float) -> np.ndarray:
+    """Frequencies changed by wavelength for contexts longer than the `original` one: with l = 2 pi / f_i, a pair keeps f_i
+    where l < original / high, takes f_i / factor where l > original / low, and in between, with s = (original / l - low) /
+    (high - low), takes (1 - s) f_i / factor + s f_i.  Returns float64 [dims / 2]; the caller rounds once to 32-bit."""
+    f = power_frequencies(base, dims)
+    wavelength = 2.0 * math.pi / f
+    s = (original / wavelength - low) / (high - low)
+    out = (1.0 - s) * f / factor + s * f
+    out = np.where(wavelength < original / high, f, out)
+    return np.where(wavelength > original / low, f / factor, out)
+
+
 class NoPositionEncoding(Part):
     cos = None
     sin = None

@@ -94,3 +94,4 @@ def _ensure_builtin() -> None:
     from .models import buzetar as _buzetar  # noqa: F401
     from .models import kisepel as _kisepel  # noqa: F401
     from .models import zamizen as _zamizen  # noqa: F401
+    from .models import nomutar as _nomutar  # noqa: F401
