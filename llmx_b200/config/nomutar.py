@@ -221,7 +221,7 @@ class NomutarConfig(ModelConfig):
     norm_eps: float
     norm_groups: int = 1
     residual_mult: float = 1.0
-    canon_taps: int = 1                  # taps of the causal filter on a mixer's input (1: none)
+    canon_taps: int = 0                  # taps of the causal filter on a mixer's input (0: no filter)
     loop: Loop = Loop()
     embedding_scale: float = 1.0
     pair_table: Optional[PairTable] = None
@@ -259,7 +259,7 @@ class NomutarConfig(ModelConfig):
         groups = _int(norm, "groups", "norm") if "groups" in norm else 1
         if width % groups:
             raise ConfigError(f"nomutar: width ({width}) must be a multiple of norm.groups ({groups})")
-        taps = _int(_obj(raw, "canon", "config"), "taps", "canon") if raw.get("canon") is not None else 1
+        taps = _int(_obj(raw, "canon", "config"), "taps", "canon") if raw.get("canon") is not None else 0
         emb = raw.get("embedding")
         emb_scale, pairs = 1.0, None
         if emb is not None:
@@ -285,7 +285,7 @@ class NomutarConfig(ModelConfig):
                              "layers": [layer.to_dict() for layer in self.layers]}
         if self.pair_table is not None:
             d["embedding"]["bigram"] = self.pair_table.to_dict()
-        if self.canon_taps > 1:
+        if self.canon_taps > 0:
             d["canon"] = {"taps": self.canon_taps}
         if self.logit_softcap is not None:
             d["logit_softcap"] = self.logit_softcap

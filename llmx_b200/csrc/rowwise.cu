@@ -825,7 +825,7 @@ group_norm_conv_kernel(GroupNormConv a, OutT* __restrict__ h, OutT* __restrict__
         const float wc = a.w[c];
         const float cur = xrow[c] * gnc_rstd[keep * a.groups + g] * wc;
         h[(size_t)r * width + c] = from_float<OutT>(cur);
-        if (keep > 0) {
+        if (a.taps_w != nullptr) {
             float acc = 0.0f;
             for (int j = 0; j < keep; ++j) {
                 const int ii = i0 - keep + j;
@@ -836,13 +836,13 @@ group_norm_conv_kernel(GroupNormConv a, OutT* __restrict__ h, OutT* __restrict__
             }
             acc = fmaf(a.taps_w[(size_t)c * a.taps + keep], cur, acc);
             hm[(size_t)r * width + c] = from_float<OutT>(cur + acc);
-            if (s_new >= 0) fresh[(size_t)s_new * width + c] = cur;
+            if (keep > 0 && s_new >= 0) fresh[(size_t)s_new * width + c] = cur;
         }
     }
 }
 
 // x float32 [*, width]; w float32 [width]; h (and hm, with a filter) [rows, width] of `out_dtype`; taps_w float32 [width, taps]
-// or null (taps 1); state float32 [slots, slot_floats]; the step's row ranges, histories and slots as a step gives them;
+// or null (no filter; a filter of one tap keeps no state); state float32 [slots, slot_floats]; the step's row ranges, histories and slots as a step gives them;
 // zero: a float buffer of zero_count values (a multiple of 4, 16-byte aligned) cleared in passing, or null.
 LLMX_EXPORT int llmx_group_norm_conv(const float* x, const float* w, int width, int groups, float eps, const int* row_index,
                                      int rows, void* h, void* hm, int out_dtype, const float* taps_w, int taps, float* state,
@@ -852,7 +852,8 @@ LLMX_EXPORT int llmx_group_norm_conv(const float* x, const float* w, int width, 
     if (rows <= 0) return 0;
     if (width <= 0 || groups <= 0 || width % groups || taps < 1 || taps * groups > 8192) return LLMX_ERR_BAD_ARGUMENT;
     if (zero && (zero_count % 4 || ((uintptr_t)zero & 15))) return LLMX_ERR_BAD_ARGUMENT;
-    if (taps > 1 && (taps_w == nullptr || hm == nullptr || state == nullptr || row_index != nullptr || row_request == nullptr ||
+    if ((taps_w != nullptr) != (hm != nullptr) || (taps > 1 && taps_w == nullptr)) return LLMX_ERR_BAD_ARGUMENT;
+    if (taps > 1 && (state == nullptr || row_index != nullptr || row_request == nullptr ||
                      state_off + (long long)(taps - 1) * width > slot_floats))
         return LLMX_ERR_BAD_ARGUMENT;
     GroupNormConv a{x, w, width, groups, eps, row_index, rows, taps_w, taps, state, slot_floats, state_off, row_request, row_start,

@@ -64,7 +64,7 @@ def build_nomutar(cfg: NomutarConfig) -> Model:
     E = cfg.width
     blocks = []
     for layer in cfg.layers:
-        filt = InputFilter(E, cfg.canon_taps, role="") if cfg.canon_taps > 1 else None
+        filt = InputFilter(E, cfg.canon_taps, role="") if cfg.canon_taps > 0 else None
         blocks.append(ParallelBlock(GroupedRMSNorm(E, cfg.norm_eps, cfg.norm_groups, role=""), _mixer(cfg, layer.mixer),
                                     _feed_forward(cfg, layer.mlp), names=("norm1", "mix", "mlp", "canon1"),
                                     factor=cfg.residual_mult, input_filter=filt))

@@ -487,16 +487,17 @@ def group_norm_conv(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: i
     taps = 1
     if taps_w is not None:
         taps = taps_w.shape[1]
-        _need(taps_w.dtype == torch.float32 and tuple(taps_w.shape) == (width, taps), "group_norm: taps float32 [width, taps]")
+        _need(taps_w.dtype == torch.float32 and tuple(taps_w.shape) == (width, taps) and taps >= 1, "group_norm: taps float32 [width, taps]")
+        _need(filtered is not None and filtered.dtype == out.dtype and tuple(filtered.shape) == (rows, width) and row_index is None,
+              "group_norm: the filter wants a second output")
     if taps > 1:
-        _need(filtered is not None and filtered.dtype == out.dtype and tuple(filtered.shape) == (rows, width) and row_index is None
-              and step is not None and rows == step.rows, "group_norm: the filter wants a second output and the step")
+        _need(step is not None and rows == step.rows, "group_norm: the filter wants the step")
         _need(state is not None and state.dtype == torch.float32 and state.dim() == 2 and state_off + (taps - 1) * width <= state.shape[1],
               "group_norm: state slots too small for the filter's inputs")
     s = step if taps > 1 else None
     _check(_fn("rowwise", "llmx_group_norm_conv")(
-        _ptr(x), _ptr(weight), width, int(groups), float(eps), _ptr(row_index), rows, _ptr(out), _ptr(filtered if taps > 1 else None),
-        _code(out), _ptr(taps_w if taps > 1 else None), taps, _ptr(state if taps > 1 else None), 0 if s is None else state.shape[1],
+        _ptr(x), _ptr(weight), width, int(groups), float(eps), _ptr(row_index), rows, _ptr(out), _ptr(filtered if taps_w is not None else None),
+        _code(out), _ptr(taps_w), taps, _ptr(state if taps > 1 else None), 0 if s is None else state.shape[1],
         int(state_off), _ptr(s.row_request if s else None), _ptr(s.row_start if s else None), _ptr(s.row_count if s else None),
         _ptr(s.history if s else None), _ptr(s.state_slots if s else None), _ptr(s.state_slots_out if s else None),
         s.requests if s else 0, _ptr(zero), 0 if zero is None else zero.numel(), _stream()), "group_norm_conv")

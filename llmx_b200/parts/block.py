@@ -82,8 +82,8 @@ class InputFilter(Part):
     the row itself); the block that holds it applies it (`ParallelBlock(input_filter=)`) and keeps its state."""
 
     def __init__(self, width: int, taps: int, role: str = ""):
-        if taps < 2:
-            raise ValueError("input filter: at least two taps (one tap is no filter)")
+        if taps < 1:
+            raise ValueError("input filter: at least one tap")
         self.width, self.taps, self.role = int(width), int(taps), role
         self.weight: Optional[torch.Tensor] = None
 
@@ -105,7 +105,7 @@ class ParallelBlock(Part):
     into the stream.  `input_filter`: the mixer reads h + filter(h) instead of h = norm(x), a causal filter over the
     request's rows on each channel (the feed-forward reads h as it is); the norm must offer `forward_filtered`, and the
     block's cache need is then the mixer's entries and, last, a state entry of (taps - 1) * width floats (the last
-    normed rows of the request)."""
+    normed rows of the request; none for a filter of one tap)."""
 
     def __init__(self, norm: Part, mixer: Part, ffn: Optional[Part], names=("norm", "mixer", "mlp", "filter"), factor: float = 1.0,
                  input_filter: Optional[InputFilter] = None):
@@ -126,7 +126,7 @@ class ParallelBlock(Part):
 
     def cache_spec(self):
         spec = self.mixer.cache_spec()
-        if self.input_filter is None:
+        if self.input_filter is None or self.input_filter.taps == 1:     # one tap reads the row itself: nothing to keep
             return spec
         from ..cache.manager import StateSpec
         mine = StateSpec(((self.input_filter.taps - 1) * self.input_filter.width,), "float32")
@@ -152,12 +152,15 @@ class ParallelBlock(Part):
         others = [_cleared(p, rows, x.device, step) for p in (self.mixer, self.ffn) if p is not None and not hasattr(p, "stored_products")]
         filter_entry = None
         if self.input_filter is not None:
-            entries = tuple(cache_entry) if isinstance(cache_entry, (tuple, list)) else (cache_entry,)
-            writes = tuple(write_cache) if isinstance(write_cache, (tuple, list)) else (write_cache,) * len(entries)
-            filter_entry, entries, writes = entries[-1], entries[:-1], writes[:-1]
-            cache_entry = None if not entries else entries[0] if len(entries) == 1 else entries
-            write_cache = True if not writes else writes[0] if len(writes) == 1 else writes
-            h, hm = self.norm.forward_filtered(x, self.input_filter.weight, step.state(filter_entry), step, zero=flat)
+            state = None
+            if self.input_filter.taps > 1:
+                entries = tuple(cache_entry) if isinstance(cache_entry, (tuple, list)) else (cache_entry,)
+                writes = tuple(write_cache) if isinstance(write_cache, (tuple, list)) else (write_cache,) * len(entries)
+                filter_entry, entries, writes = entries[-1], entries[:-1], writes[:-1]
+                cache_entry = None if not entries else entries[0] if len(entries) == 1 else entries
+                write_cache = True if not writes else writes[0] if len(writes) == 1 else writes
+                state = step.state(filter_entry)
+            h, hm = self.norm.forward_filtered(x, self.input_filter.weight, state, step, zero=flat)
         else:
             h = hm = self.norm.forward(x, zero=flat)
         for z in others:

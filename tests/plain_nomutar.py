@@ -185,10 +185,15 @@ def gated_unit(h, gate, up, down):
     return (silu(h @ gate.astype(F).T) * (h @ up.astype(F).T)) @ down.astype(F).T
 
 
-def routed_experts(h, w, prefix, experts, top):
-    """Each row's `top` experts by the largest router logits, weighted by the softmax over those logits alone."""
+def routed_experts(h, w, prefix, experts, top, margins=None):
+    """Each row's `top` experts by the largest router logits, weighted by the softmax over those logits alone.
+    `margins`, a list, receives per row how far the last chosen logit lies above the first one left out, as a fraction
+    of the spread (standard deviation) of the row's logits."""
     z = h @ w[prefix + "router"].astype(F).T + w[prefix + "router.b"].astype(F)
     out = np.zeros_like(h)
+    if margins is not None:
+        ranked = -np.sort(-z, axis=1)
+        margins.append((ranked[:, top - 1] - ranked[:, top]) / (z.std(axis=1) + 1e-30) if top < experts else np.full(h.shape[0], np.inf))
     for t in range(h.shape[0]):
         chosen = np.argsort(-z[t], kind="stable")[:top]
         p = np.exp(z[t, chosen] - z[t, chosen].max())
@@ -198,10 +203,10 @@ def routed_experts(h, w, prefix, experts, top):
     return out
 
 
-def feed_forward(h, w, prefix, mlp):
+def feed_forward(h, w, prefix, mlp, margins=None):
     if mlp["kind"] == "dense":
         return gated_unit(h, w[prefix + "gate"], w[prefix + "up"], w[prefix + "down"])
-    out = routed_experts(h, w, prefix, mlp["router"]["experts"], mlp["router"]["top"])
+    out = routed_experts(h, w, prefix, mlp["router"]["experts"], mlp["router"]["top"], margins)
     if mlp.get("shared") is not None:
         s = prefix + "shared."
         out = out + gated_unit(h, w[s + "gate"], w[s + "up"], w[s + "down"]) * sigmoid(h @ w[s + "sg"].astype(F).T)
@@ -217,20 +222,22 @@ def layer_order(cfg):
     return order + list(range(loop["stop"], n))
 
 
-def forward(cfg, w, tokens, streams=None):
-    """Logits [T, vocab] of a whole sequence; `streams`, a list, receives the residual stream after every layer run."""
+def forward(cfg, w, tokens, streams=None, margins=None):
+    """Logits [T, vocab] of a whole sequence; `streams`, a list, receives the residual stream after every layer run;
+    `margins`, a list, one array [T] per routed feed-forward run: the margin of each row's choice of experts."""
     eps, groups, mult = cfg["norm"]["eps"], cfg["norm"]["groups"], cfg.get("residual_mult", 1.0)
     emb = cfg.get("embedding") or {}
     bi = emb.get("bigram")
+    taps = (cfg.get("canon") or {}).get("taps", 0)
     x = embed(tokens, w["embed"], emb.get("scale", 1.0), w["bigram"] if bi else None,
               *((bi["buckets"], bi["mul_prev"], bi["mul_cur"]) if bi else ()))
     for i in layer_order(cfg):
         layer, p = cfg["layers"][i], f"l{i}."
         h = grouped_rms_norm(x, w[p + "norm1"], eps, groups)
-        hm = h + causal_filter(h, w[p + "canon1"]) if (p + "canon1") in w else h
+        hm = h + causal_filter(h, w[p + "canon1"]) if taps else h
         y = attention_mixer(hm, w, p + "mix.", layer["mixer"], layer["type"], eps)
         if layer.get("mlp") is not None:
-            y = y + feed_forward(h, w, p + "mlp.", layer["mlp"])
+            y = y + feed_forward(h, w, p + "mlp.", layer["mlp"], margins)
         x = x + mult * y
         if streams is not None:
             streams.append(x.copy())
