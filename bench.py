@@ -131,6 +131,11 @@ def reference_arm(args):
 # `--design zamizen`: a Zamizen of as many layers (two latent layers, then a layer of grouped-query attention with a
 # four-tap filter; every second such layer reads the keys and values of the one before it) beside the two models that
 # have its kernels' nearest relatives: a Buzetar whose layers are all latent attention without a window, and a Qwen3.
+# `--design nomutar`: a Nomutar of as many layers (its three attentions in turn: neighbouring pairs with biases under a window,
+# rotated values with a learned sink under a window, causal over everything; heads of 128, a quarter as many key/value
+# heads; the first layer's feed-forward dense, the others' Kisepel's experts with a router; a four-tap input filter, four norm
+# groups, a pair table of 16,381 buckets) beside the two models that have its kernels' nearest relatives: a Zamizen whose
+# layers are all grouped-query attention (the same attention kernels, a filter, a factor on the residual) and the Kisepel.
 DESIGN_SIZES = {
     "w2048": dict(width=2048, heads=16, ff=6144, vocab=32768, q_rank=768, kv_rank=512, rot=64, window=2048, layers=6),
     "w4096": dict(width=4096, heads=32, ff=12288, vocab=32768, q_rank=1536, kv_rank=512, rot=64, window=4096, layers=3),
@@ -144,7 +149,7 @@ def design_bench(args) -> int:
     import statistics
     import torch
     from llmx_b200 import ops
-    from llmx_b200.config import BuzetarConfig, KisepelConfig, Qwen3Config, ZamizenConfig
+    from llmx_b200.config import BuzetarConfig, KisepelConfig, NomutarConfig, Qwen3Config, ZamizenConfig
     from llmx_b200.engine import Engine, EngineOptions, StepEntry
     from llmx_b200.engine.decode_loop import DecodeSession
     torch.cuda.set_device(0)
@@ -212,6 +217,24 @@ def design_bench(args) -> int:
             buz_latent = BuzetarConfig.from_dict({"architecture": "Buzetar", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
                                                   "logit_scale": 1.0, "layers": [all_latent] * L})
             runs = (("zamizen", zam), ("buzetar_latent", buz_latent), ("qwen3", qwen))
+        if args.design == "nomutar":
+            G = max(H // 4, 1)
+            head = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+            ramp = {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+            bands = {"base": 50000.0, "dims": 64, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}}
+            nom_kinds = [
+                {"type": "attention_2", "mixer": dict(head, rot=ramp, mask={"size": z["window"]}, softcap=50.0)},
+                {"type": "attention", "mixer": dict(head, rot=bands, mask={"size": z["window"]}, softcap=20.0)},
+                {"type": "attention_3", "mixer": dict(head, rot={"base": 10000.0, "dims": 64})}]
+            nom = NomutarConfig.from_dict({
+                "architecture": "Nomutar", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5, "groups": 4}, "residual_mult": 0.7,
+                "canon": {"taps": 4}, "embedding": {"scale": float(E) ** 0.5, "bigram": {"buckets": 16381, "mul_prev": 127, "mul_cur": 7}},
+                "logit_softcap": 30.0,
+                "layers": [dict(nom_kinds[i % 3], mlp={"kind": "dense", "ff": F} if i == 0 else experts) for i in range(L)]})
+            gqa = dict(head, conv=4, rot={"base": 1000000.0, "dims": 64})
+            zam_attention = ZamizenConfig.from_dict({"architecture": "Zamizen", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5}, "residual_mult": 0.7,
+                                                     "layers": [{"type": "attention", "mixer": gqa, "mlp": {"kind": "dense", "ff": F}}] * L})
+            runs = (("nomutar", nom), ("zamizen_attention", zam_attention), ("kisepel", kis))
         res = {"config": dict(z)}
         out["sizes"][name] = res                                # filled as the arms end, so that a run that stops early says what it has
         for tag, cfg in runs:
@@ -292,10 +315,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--only", choices=["decode", "prefill", "sample"], default=None,
                     help="run one part only (for profiling); the line then holds only that part")
-    ap.add_argument("--design", choices=["buzetar", "kisepel", "zamizen"], default=None,
+    ap.add_argument("--design", choices=["buzetar", "kisepel", "zamizen", "nomutar"], default=None,
                     help="instead of the default workload: prompt and decode throughput of this design at sizes that resemble a "
                          "real model's layers, beside the closest other design of equal size (Buzetar beside Qwen3, Kisepel beside Buzetar, "
-                         "Zamizen beside an all-latent Buzetar and Qwen3; one JSON line of its own)")
+                         "Zamizen beside an all-latent Buzetar and Qwen3, Nomutar beside an all-attention Zamizen and Kisepel; one JSON line of its own)")
     ap.add_argument("--design-size", default=None, help="with --design: one of " + ", ".join(sorted(DESIGN_SIZES)) + " (default: all)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -376,50 +376,95 @@ __global__ void combine_weighted_kernel(const float* __restrict__ y, float* __re
 
 // A router: logits z = h W^T + b in 32-bit (h may be bfloat16; the weights are 32-bit), the `top` largest (the lower index
 // first among equals), and as weights the softmax over the chosen logits alone.  `extra` more rows of W after the experts'
-// give one number a row each through a sigmoid (a gate on a part that runs beside the experts).  One block a row; a warp
-// makes one logit, lanes in a fixed order.
-template <typename T>
-__global__ void __launch_bounds__(128)
-router_kernel(const T* __restrict__ h, const float* __restrict__ w, const float* __restrict__ bias, int K, int experts, int top,
-              int extra, int* __restrict__ choice, float* __restrict__ weight, float* __restrict__ gate) {
+// give one number a row each through a sigmoid (a gate on a part that runs beside the experts).  A block takes R rows of
+// the step (1 when the rows are few, so that they spread over the SMs; 8 when they are many, so that a weight row is read
+// once for 8 rows); a warp makes one logit of each of the block's rows, lanes reading 16-byte pieces in a fixed order, so a
+// row's logits do not depend on what else the step holds.
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+    v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+}
+
+template <typename T, int R>
+__global__ void __launch_bounds__(256)
+router_kernel(const T* __restrict__ h, const float* __restrict__ w, const float* __restrict__ bias, int rows, int K, int experts,
+              int top, int extra, int* __restrict__ choice, float* __restrict__ weight, float* __restrict__ gate) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float router_z[];                    // [experts + extra]
-    const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const T* x = h + (size_t)row * K;
-    for (int e = warp; e < experts + extra; e += 4) {
+    extern __shared__ float router_z[];                    // [R][experts + extra]
+    const int row0 = blockIdx.x * R, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int outs = experts + extra;
+    const bool vec = (K & 3) == 0;
+    for (int e = warp; e < outs; e += 8) {
         const float* we = w + (size_t)e * K;
-        float s = 0.0f;
-        for (int k = lane; k < K; k += 32) s = fmaf(to_float(x[k]), we[k], s);
-        s = warp_sum(s);
-        if (lane == 0) router_z[e] = s + ((bias && e < experts) ? bias[e] : 0.0f);
+        float s[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) s[r] = 0.0f;
+        if (vec) {
+#pragma unroll 2
+            for (int k = 4 * lane; k < K; k += 128) {
+                float wv[4];
+                load4(we + k, wv);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    if (row0 + r < rows) {
+                        float xv[4];
+                        load4(h + (size_t)(row0 + r) * K + k, xv);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) s[r] = fmaf(xv[i], wv[i], s[r]);
+                    }
+                }
+            }
+        } else {
+            for (int k = lane; k < K; k += 32)
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    if (row0 + r < rows) s[r] = fmaf(to_float(h[(size_t)(row0 + r) * K + k]), we[k], s[r]);
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float t = warp_sum(s[r]);
+            if (lane == 0) router_z[r * outs + e] = t + ((bias && e < experts) ? bias[e] : 0.0f);
+        }
     }
     __syncthreads();
-    if (threadIdx.x < extra) gate[(size_t)row * extra + threadIdx.x] = 1.0f / (1.0f + expf(-router_z[experts + threadIdx.x]));
-    if (threadIdx.x != 0) return;
+    for (int i = threadIdx.x; i < R * extra; i += blockDim.x) {
+        const int r = i / extra, x = i - r * extra;
+        if (row0 + r < rows) gate[(size_t)(row0 + r) * extra + x] = 1.0f / (1.0f + expf(-router_z[r * outs + experts + x]));
+    }
+    if (threadIdx.x >= R || row0 + (int)threadIdx.x >= rows) return;
+    const float* z = router_z + threadIdx.x * outs;
+    int* mine = choice + (size_t)(row0 + threadIdx.x) * top;
+    float* wt = weight + (size_t)(row0 + threadIdx.x) * top;
     float zmax = 0.0f;
     for (int k = 0; k < top; ++k) {
         int best = -1;
         float bz = 0.0f;
         for (int e = 0; e < experts; ++e) {
-            const float z = router_z[e];
-            if (z != z) continue;                            // a logit that is no number is never chosen
+            const float ze = z[e];
+            if (ze != ze) continue;                          // a logit that is no number is never chosen
             bool taken = false;
-            for (int j = 0; j < k; ++j) taken |= choice[(size_t)row * top + j] == e;
-            if (!taken && (best < 0 || z > bz)) best = e, bz = z;
+            for (int j = 0; j < k; ++j) taken |= mine[j] == e;
+            if (!taken && (best < 0 || ze > bz)) best = e, bz = ze;
         }
         if (best < 0) best = 0, bz = -INFINITY;
-        choice[(size_t)row * top + k] = best;
-        weight[(size_t)row * top + k] = bz;
+        mine[k] = best;
+        wt[k] = bz;
         if (k == 0) zmax = bz;
     }
     float sum = 0.0f;
     for (int k = 0; k < top; ++k) {
-        const float e = expf(weight[(size_t)row * top + k] - zmax);
-        weight[(size_t)row * top + k] = e;
+        const float e = expf(wt[k] - zmax);
+        wt[k] = e;
         sum += e;
     }
-    for (int k = 0; k < top; ++k) weight[(size_t)row * top + k] /= sum;
+    for (int k = 0; k < top; ++k) wt[k] /= sum;
 }
 
 inline int max_tiles(int pairs, int experts, int tile_rows) { return (pairs + tile_rows - 1) / tile_rows + experts; }
@@ -431,15 +476,23 @@ LLMX_EXPORT int llmx_moe_router(const void* h, int dtype, const float* w, const 
                                 int extra, int* choice, float* weight, float* gate, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (K <= 0 || experts <= 0 || top <= 0 || top > experts || extra < 0 || extra > 128 || (extra > 0 && gate == nullptr) ||
-        (size_t)(experts + extra) * sizeof(float) > 48 * 1024)
+        experts + extra > 1024)
         return LLMX_ERR_BAD_ARGUMENT;
-    const size_t smem = (size_t)(experts + extra) * sizeof(float);
-    if (dtype == LLMX_BF16)
-        launch_kernel(router_kernel<__nv_bfloat16>, dim3(rows), dim3(128), smem, stream, (const __nv_bfloat16*)h, w, bias, K, experts, top, extra, choice, weight, gate);
-    else if (dtype == LLMX_F32)
-        launch_kernel(router_kernel<float>, dim3(rows), dim3(128), smem, stream, (const float*)h, w, bias, K, experts, top, extra, choice, weight, gate);
-    else
-        return LLMX_ERR_UNSUPPORTED;
+    // Rows of 16-byte pieces need aligned rows; else the scalar walk.
+    const bool many = rows > 64;
+    const int R = many ? 8 : 1;
+    const size_t smem = (size_t)R * (experts + extra) * sizeof(float);
+    if (smem > 48 * 1024) return LLMX_ERR_UNSUPPORTED;
+    const dim3 grid((rows + R - 1) / R);
+    if ((K & 3) == 0 && (((uintptr_t)h & 15) || ((uintptr_t)w & 15))) return LLMX_ERR_BAD_ARGUMENT;
+#define LLMX_ROUTER(T, RR) \
+    launch_kernel(router_kernel<T, RR>, grid, dim3(256), smem, stream, (const T*)h, w, bias, rows, K, experts, top, extra, choice, weight, gate)
+    if (dtype == LLMX_BF16 && many) LLMX_ROUTER(__nv_bfloat16, 8);
+    else if (dtype == LLMX_BF16) LLMX_ROUTER(__nv_bfloat16, 1);
+    else if (dtype == LLMX_F32 && many) LLMX_ROUTER(float, 8);
+    else if (dtype == LLMX_F32) LLMX_ROUTER(float, 1);
+    else return LLMX_ERR_UNSUPPORTED;
+#undef LLMX_ROUTER
     return launch_status();
 }
 

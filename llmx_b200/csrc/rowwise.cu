@@ -762,7 +762,20 @@ struct GroupNormConv {
     long long zero_count;
 };
 
-template <typename OutT>
+template <int VEC> __device__ __forceinline__ void load_run(const float* p, float (&v)[VEC]) {
+    if constexpr (VEC == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    } else {
+        v[0] = p[0];
+    }
+}
+template <typename T, int VEC> __device__ __forceinline__ void store_run(T* p, const float (&v)[VEC]) {
+    if constexpr (VEC == 4) store4(p, v[0], v[1], v[2], v[3]);
+    else p[0] = from_float<T>(v[0]);
+}
+
+template <typename OutT, int VEC>
 __global__ void __launch_bounds__(256)
 group_norm_conv_kernel(GroupNormConv a, OutT* __restrict__ h, OutT* __restrict__ hm) {
     pdl_trigger();
@@ -807,36 +820,66 @@ group_norm_conv_kernel(GroupNormConv a, OutT* __restrict__ h, OutT* __restrict__
     }
     const int part = width / a.groups;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const bool vec = (part & 3) == 0 && !((uintptr_t)a.x & 15);             // 16-byte pieces (one order of sums a width)
     for (int item = warp; item < a.taps * a.groups; item += warps) {
         const int j = item / a.groups, g = item - j * a.groups;
         const int ii = i0 - keep + j;
         if (j < keep && ii < 0) continue;                    // not a row of this step
         const float* xr = a.x + (size_t)(j == keep ? src_row : first + ii) * width + (size_t)g * part;
         float ss = 0.0f;
-        for (int c = lane; c < part; c += 32) ss = fmaf(xr[c], xr[c], ss);
+        if (vec) {
+            for (int c = 4 * lane; c < part; c += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(xr + c);
+                ss = fmaf(v.x, v.x, ss);
+                ss = fmaf(v.y, v.y, ss);
+                ss = fmaf(v.z, v.z, ss);
+                ss = fmaf(v.w, v.w, ss);
+            }
+        } else
+            for (int c = lane; c < part; c += 32) ss = fmaf(xr[c], xr[c], ss);
         ss = warp_sum(ss);
         if (lane == 0) gnc_rstd[item] = 1.0f / sqrtf(ss / (float)part + a.eps);
     }
     __syncthreads();
     const float* xrow = a.x + (size_t)src_row * width;
     const int s_new = i0 - (n - keep);                       // the place of this row in the state the step leaves
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    // VEC channels a thread and turn (4 where rows, weights and outputs can be read and written in 16-byte pieces: the
+    // channels of a piece lie in one part).
+    for (int c = VEC * threadIdx.x; c < width; c += VEC * blockDim.x) {
         const int g = c / part;
-        const float wc = a.w[c];
-        const float cur = xrow[c] * gnc_rstd[keep * a.groups + g] * wc;
-        h[(size_t)r * width + c] = from_float<OutT>(cur);
+        float xv[VEC], wc[VEC], cur[VEC];
+        load_run<VEC>(xrow + c, xv);
+        load_run<VEC>(a.w + c, wc);
+        const float rr = gnc_rstd[keep * a.groups + g];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) cur[i] = xv[i] * rr * wc[i];
+        store_run<OutT, VEC>(h + (size_t)r * width + c, cur);
         if (a.taps_w != nullptr) {
-            float acc = 0.0f;
+            float acc[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
             for (int j = 0; j < keep; ++j) {
                 const int ii = i0 - keep + j;
-                float v = 0.0f;
-                if (ii >= 0) v = a.x[(size_t)(first + ii) * width + c] * gnc_rstd[j * a.groups + g] * wc;
-                else if (hist + ii >= 0) v = old[(size_t)(keep + ii) * width + c];
-                acc = fmaf(a.taps_w[(size_t)c * a.taps + j], v, acc);
+                float v[VEC];
+                if (ii >= 0) {
+                    load_run<VEC>(a.x + (size_t)(first + ii) * width + c, v);
+                    const float rj = gnc_rstd[j * a.groups + g];
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) v[i] = v[i] * rj * wc[i];
+                } else if (hist + ii >= 0) {
+                    load_run<VEC>(old + (size_t)(keep + ii) * width + c, v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) v[i] = 0.0f;
+                }
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] = fmaf(a.taps_w[(size_t)(c + i) * a.taps + j], v[i], acc[i]);
             }
-            acc = fmaf(a.taps_w[(size_t)c * a.taps + keep], cur, acc);
-            hm[(size_t)r * width + c] = from_float<OutT>(cur + acc);
-            if (keep > 0 && s_new >= 0) fresh[(size_t)s_new * width + c] = cur;
+            float out[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) out[i] = cur[i] + fmaf(a.taps_w[(size_t)(c + i) * a.taps + keep], cur[i], acc[i]);
+            store_run<OutT, VEC>(hm + (size_t)r * width + c, out);
+            if (keep > 0 && s_new >= 0) store_run<float, VEC>(fresh + (size_t)s_new * width + c, cur);
         }
     }
 }
@@ -862,10 +905,17 @@ LLMX_EXPORT int llmx_group_norm_conv(const float* x, const float* w, int width, 
     zero_blocks = zero_blocks > 1024 ? 1024 : zero_blocks;
     const dim3 grid((unsigned)(rows + (taps > 1 ? requests : 0) + zero_blocks));
     const size_t smem = (size_t)taps * groups * sizeof(float);
-    if (out_dtype == LLMX_BF16)
-        launch_kernel(group_norm_conv_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, a, (__nv_bfloat16*)h, (__nv_bfloat16*)hm);
+    // 16-byte pieces where every row, weight, output and state row starts on one and a piece lies within one part.
+    const bool vec = (width / groups) % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)w & 15) && !((uintptr_t)h & 15) && !((uintptr_t)hm & 15) &&
+                     (taps == 1 || (!((uintptr_t)state & 15) && slot_floats % 4 == 0 && state_off % 4 == 0));
+    if (out_dtype == LLMX_BF16 && vec)
+        launch_kernel(group_norm_conv_kernel<__nv_bfloat16, 4>, grid, dim3(256), smem, stream, a, (__nv_bfloat16*)h, (__nv_bfloat16*)hm);
+    else if (out_dtype == LLMX_BF16)
+        launch_kernel(group_norm_conv_kernel<__nv_bfloat16, 1>, grid, dim3(256), smem, stream, a, (__nv_bfloat16*)h, (__nv_bfloat16*)hm);
+    else if (out_dtype == LLMX_F32 && vec)
+        launch_kernel(group_norm_conv_kernel<float, 4>, grid, dim3(256), smem, stream, a, (float*)h, (float*)hm);
     else if (out_dtype == LLMX_F32)
-        launch_kernel(group_norm_conv_kernel<float>, grid, dim3(256), smem, stream, a, (float*)h, (float*)hm);
+        launch_kernel(group_norm_conv_kernel<float, 1>, grid, dim3(256), smem, stream, a, (float*)h, (float*)hm);
     else
         return LLMX_ERR_UNSUPPORTED;
     return launch_status();
@@ -940,10 +990,31 @@ __global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__
     x[i] = fmaf(f, y[i], x[i]);
 }
 
+__global__ void add_rows_vec_kernel(float4* __restrict__ x, const float4* __restrict__ y, const float* __restrict__ row_factor,
+                                    float factor, int width4, long long total4) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const float f = row_factor ? factor * row_factor[i / width4] : factor;
+    float4 a = x[i];
+    const float4 b = y[i];
+    a.x = fmaf(f, b.x, a.x);
+    a.y = fmaf(f, b.y, a.y);
+    a.z = fmaf(f, b.z, a.z);
+    a.w = fmaf(f, b.w, a.w);
+    x[i] = a;
+}
+
 LLMX_EXPORT int llmx_add_rows(float* x, const float* y, const float* row_factor, float factor, int rows, int width,
                               cudaStream_t stream) {
     if (rows <= 0) return 0;
     const long long total = (long long)rows * width;
+    if (width % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)y & 15)) {
+        launch_kernel(add_rows_vec_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, (float4*)x, (const float4*)y,
+                      row_factor, factor, width / 4, total / 4);
+        return launch_status();
+    }
     launch_kernel(add_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, y, row_factor, factor, width, total);
     return launch_status();
 }
