@@ -440,6 +440,180 @@ attention_merge_kernel(const float* __restrict__ partial, QT* __restrict__ out, 
     }
 }
 
+// ---- the staged form, for rows that are few -------------------------------------------------------------------------------
+// A block of four warps takes one row, one key/value head and one of `splits` ranges of the row's keys, and serves all
+// query heads of the group from one read of the keys: tiles of TK [key ; value] rows are copied from their pages into two
+// buffers of shared memory by cp.async (16-byte pieces, the next tile in flight while this one is used; rows padded by
+// one piece, so that lanes reading 16-byte pieces of 32 different rows meet in no bank).  Warp w serves heads w, w + 4, ...:
+// a lane makes the whole score of one key (no shuffles within a key), the tile's maximum and sum meet once a tile, the
+// 32-bit weights lie in shared memory and every lane adds them over its columns of the values.  Every (row, head, range)
+// leaves sum, maximum and weight in `partial`, which the merge kernel above finishes (sink, division, turning back).
+template <typename T> struct Piece;
+template <> struct Piece<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    }
+};
+template <> struct Piece<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+            v[2 * i] = f.x, v[2 * i + 1] = f.y;
+        }
+    }
+};
+
+template <typename T, int HPW, int VPL>
+__global__ void __launch_bounds__(128)
+attention_staged_kernel(const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ row_request,
+                        const int* __restrict__ positions, const int* __restrict__ block_tables, int table_stride, int heads,
+                        int kv_heads, int D, int V, int page_size, int window, int chunk, float scale, int splits, int TK,
+                        float softcap, float* __restrict__ partial) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char st_smem[];
+    constexpr int EP = Piece<T>::N;
+    const int row = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+    const int ratio = heads / kv_heads, W = D + V, ws = W + EP, pieces = W / EP;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* qs = reinterpret_cast<float*>(st_smem);               // [ratio][D]
+    float* ps = qs + (size_t)ratio * D;                          // [ratio][TK]
+    T* kv = reinterpret_cast<T*>(ps + (size_t)ratio * TK);       // [2][TK][ws]
+    const int pos = positions[row];
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
+    const int per = (pos - lo + splits) / splits;
+    const int first = lo + split * per, last = min(pos, first + per - 1);
+    const int n_tiles = first <= last ? (last - first + TK) / TK : 0;
+    const int* table = block_tables + (size_t)row_request[row] * table_stride;
+    auto issue = [&](int tile, int which) {
+        T* buf = kv + (size_t)which * TK * ws;
+        const int kt0 = first + tile * TK;
+        for (int i = threadIdx.x; i < TK * pieces; i += 128) {
+            const int j = i / pieces, c = i - j * pieces;
+            const int t = kt0 + j;
+            const bool real = t <= last;
+            const T* src = cache;
+            if (real) src = cache + (((size_t)table[t / page_size] * kv_heads + g) * page_size + t % page_size) * (size_t)W + (size_t)c * EP;
+            const int bytes = real ? 16 : 0;                         // no key here: the piece is filled with zeros
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(buf + (size_t)j * ws + c * EP)),
+                         "l"(src), "r"(bytes) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (n_tiles > 0) issue(0, 0);
+    for (int i = threadIdx.x; i < ratio * D; i += 128) qs[i] = to_float(q[((size_t)row * heads + (size_t)g * ratio) * D + i]);
+    float m[HPW], l[HPW], acc[HPW][VPL];
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        m[hh] = -INFINITY;
+        l[hh] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc[hh][i] = 0.0f;
+    }
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                 // this tile has landed (and the queries); everyone has left the other buffer
+        if (tile + 1 < n_tiles) issue(tile + 1, (tile + 1) & 1);
+        const T* buf = kv + (size_t)(tile & 1) * TK * ws;
+        const int kt0 = first + tile * TK;
+        const int n_here = min(TK, last - kt0 + 1);
+#pragma unroll
+        for (int hh = 0; hh < HPW; ++hh) {
+            const int hl = warp + 4 * hh;                // the head of the group this warp serves now
+            if (hl >= ratio) break;
+            const float* qh = qs + (size_t)hl * D;
+            float* ph = ps + (size_t)hl * TK;
+            float mx = -INFINITY;
+            for (int kt = lane; kt < TK; kt += 32) {
+                const T* kr = buf + (size_t)kt * ws;
+                float s = 0.0f;
+                for (int d = 0; d < D; d += EP) {
+                    float kvv[EP];
+                    Piece<T>::load(kr + d, kvv);
+#pragma unroll
+                    for (int i = 0; i < EP; i += 4) {
+                        const float4 qv = *reinterpret_cast<const float4*>(qh + d + i);
+                        s = fmaf(qv.x, kvv[i], s);
+                        s = fmaf(qv.y, kvv[i + 1], s);
+                        s = fmaf(qv.z, kvv[i + 2], s);
+                        s = fmaf(qv.w, kvv[i + 3], s);
+                    }
+                }
+                s *= scale;
+                if (softcap > 0.0f) s = softcap * tanhf(s / softcap);
+                s = kt < n_here ? s : -INFINITY;
+                ph[kt] = s;
+                mx = fmaxf(mx, s);
+            }
+            mx = warp_max(mx);
+            const float m_new = fmaxf(m[hh], mx);        // finite: a tile holds at least one key
+            const float corr = expf(m[hh] - m_new);      // exp(-inf) = 0 before the first tile
+            m[hh] = m_new;
+            float lsum = 0.0f;
+            for (int kt = lane; kt < TK; kt += 32) {
+                const float e = expf(ph[kt] - m_new);
+                ph[kt] = e;
+                lsum += e;
+            }
+            l[hh] = l[hh] * corr + lsum;                 // per lane; the lanes meet at the end
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) acc[hh][i] *= corr;
+            __syncwarp();
+            for (int key = 0; key < n_here; ++key) {
+                const float e = ph[key];
+                const T* vr = buf + (size_t)key * ws + D;
+#pragma unroll
+                for (int i = 0; i < VPL; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < V) acc[hh][i] = fmaf(e, to_float(vr[c]), acc[hh][i]);
+                }
+            }
+            __syncwarp();                                // the weights are written again at the next tile
+        }
+    }
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        const int hl = warp + 4 * hh;
+        if (hl >= ratio) break;
+        const float lt = warp_sum(l[hh]);
+        float* prow = partial + (((size_t)row * heads + (size_t)g * ratio + hl) * splits + split) * (size_t)(V + 2);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int c = lane + 32 * i;
+            if (c < V) prow[c] = acc[hh][i];
+        }
+        if (lane == 0) {
+            prow[V] = m[hh];
+            prow[V + 1] = lt;
+        }
+    }
+}
+
+// The tile of keys the staged form takes for these sizes (the largest of 64, 32, 16 whose buffers fit), or 0 when it does
+// not take them: equal types of queries and cache, key and whole-row widths in 16-byte pieces, at most 16 heads a group.
+static int staged_tile(int q_dtype, int cache_dtype, int heads, int kv_heads, int D, int V, size_t* smem_out) {
+    if (q_dtype != cache_dtype || (q_dtype != LLMX_BF16 && q_dtype != LLMX_F32)) return 0;
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16 || D <= 0 || V <= 0 || V > 512 || D > 512) return 0;
+    const int ep = q_dtype == LLMX_BF16 ? 8 : 4, es = q_dtype == LLMX_BF16 ? 2 : 4;
+    if (D % ep || (D + V) % ep) return 0;
+    const int ratio = heads / kv_heads;
+    for (int tk = 64; tk >= 16; tk /= 2) {
+        const size_t smem = ((size_t)ratio * D + (size_t)ratio * tk) * 4 + 2 * (size_t)tk * (D + V + ep) * es;
+        if (smem <= 72 * 1024) {
+            if (smem_out) *smem_out = smem;
+            return tk;
+        }
+    }
+    return 0;
+}
+
 // ---- the tiled form, on the tensor cores ----------------------------------------------------------------------------
 // bfloat16 queries and cache, D and V multiples of 16.  A block of four warps takes 64 rows that share their keys: TOK
 // tokens in a row of one request times the R_PAD heads (the group's head count rounded up to a power of two) of one
@@ -820,4 +994,58 @@ LLMX_EXPORT int llmx_attention_tiled(const void* q, const void* cache, void* out
     if (V <= 128) LLMX_TILED(16);
     LLMX_TILED(32);
 #undef LLMX_TILED
+}
+
+// Whether the staged form takes these types and sizes.
+LLMX_EXPORT int llmx_attention_staged_fits(int q_dtype, int cache_dtype, int heads, int kv_heads, int D, int V) {
+    return staged_tile(q_dtype, cache_dtype, heads, kv_heads, D, V, nullptr) > 0;
+}
+
+// The staged form with its merge: arguments as `llmx_attention_split`; `partial` float32 [rows, heads, splits, V + 2] is
+// needed whatever `splits` is.
+LLMX_EXPORT int llmx_attention_staged(const void* q, int q_dtype, const void* cache, int cache_dtype, void* out,
+                                      const int* row_request, const int* positions, const int* block_tables, int table_stride,
+                                      int rows, int heads, int kv_heads, int D, int V, int page_size, int window, int chunk,
+                                      float scale, int splits, float* partial, float softcap, const float* sink, int sink_mode,
+                                      const float* vfreq, int v_neighbours, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    size_t smem = 0;
+    const int tk = staged_tile(q_dtype, cache_dtype, heads, kv_heads, D, V, &smem);
+    if (tk == 0 || kv_heads > 65535 || ((uintptr_t)cache & 15)) return LLMX_ERR_UNSUPPORTED;
+    if (splits < 1 || splits > 64 || partial == nullptr || page_size <= 0) return LLMX_ERR_BAD_ARGUMENT;
+    if (sink_mode < 0 || sink_mode > 2 || (sink_mode == 1 && sink == nullptr) || (vfreq != nullptr && V % 2)) return LLMX_ERR_BAD_ARGUMENT;
+    const AttnExtras extras{softcap, sink, sink_mode, vfreq, v_neighbours};
+    const dim3 grid(rows, kv_heads, splits);
+    const int hpw = (heads / kv_heads + 3) / 4;
+#define LLMX_STAGED(T, H, VL)                                                                                              \
+    do {                                                                                                                    \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_staged_kernel<T, H, VL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_kernel(attention_staged_kernel<T, H, VL>, grid, dim3(128), smem, stream, (const T*)q, (const T*)cache, row_request, \
+                      positions, block_tables, table_stride, heads, kv_heads, D, V, page_size, window, chunk, scale, splits, tk, \
+                      softcap, partial);                                                                                    \
+    } while (0)
+#define LLMX_STAGED_T(T)                                                                                                   \
+    do {                                                                                                                    \
+        if (V <= 128) {                                                                                                     \
+            if (hpw == 1) LLMX_STAGED(T, 1, 4);                                                                             \
+            else if (hpw == 2) LLMX_STAGED(T, 2, 4);                                                                        \
+            else LLMX_STAGED(T, 4, 4);                                                                                      \
+        } else {                                                                                                            \
+            if (hpw == 1) LLMX_STAGED(T, 1, 16);                                                                            \
+            else if (hpw == 2) LLMX_STAGED(T, 2, 16);                                                                       \
+            else LLMX_STAGED(T, 4, 16);                                                                                     \
+        }                                                                                                                   \
+    } while (0)
+    if (q_dtype == LLMX_BF16) LLMX_STAGED_T(__nv_bfloat16);
+    else LLMX_STAGED_T(float);
+#undef LLMX_STAGED_T
+#undef LLMX_STAGED
+    int status = launch_status();
+    if (status) return status;
+    const int items = rows * heads;
+    if (q_dtype == LLMX_BF16)
+        launch_kernel(attention_merge_kernel<__nv_bfloat16>, dim3((items + 3) / 4), dim3(128), (size_t)4 * V * sizeof(float), stream, (const float*)partial, (__nv_bfloat16*)out, items, V, splits, heads, positions, extras);
+    else
+        launch_kernel(attention_merge_kernel<float>, dim3((items + 3) / 4), dim3(128), (size_t)4 * V * sizeof(float), stream, (const float*)partial, (float*)out, items, V, splits, heads, positions, extras);
+    return launch_status();
 }

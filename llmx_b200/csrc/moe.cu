@@ -407,7 +407,7 @@ router_kernel(const T* __restrict__ h, const float* __restrict__ w, const float*
 #pragma unroll
         for (int r = 0; r < R; ++r) s[r] = 0.0f;
         if (vec) {
-#pragma unroll 2
+#pragma unroll 4
             for (int k = 4 * lane; k < K; k += 128) {
                 float wv[4];
                 load4(we + k, wv);

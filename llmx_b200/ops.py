@@ -114,6 +114,9 @@ _SIGNATURES = {
                                              _f, _p, _i, _i, _p, _p, _p, _i, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _p, _p],
     ("attention_split", "llmx_attention_split"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p,
                                                   _f, _p, _i, _p, _i, _p],
+    ("attention_split", "llmx_attention_staged"): [_p, _i, _p, _i, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p,
+                                                   _f, _p, _i, _p, _i, _p],
+    ("attention_split", "llmx_attention_staged_fits"): [_i, _i, _i, _i, _i, _i],
     ("attention_split", "llmx_attention_tiled_fits"): [_i, _i, _i, _i],
     ("attention_split", "llmx_attention_tiled"): [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f,
                                                   _f, _p, _i, _p, _i, _p],
@@ -734,11 +737,13 @@ NO_EXTRAS = SoftmaxExtras()
 def attention_split(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row_request: torch.Tensor,
                     positions: torch.Tensor, block_tables: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
                     value_dim: int, window: Optional[int], chunk: Optional[int], scale: float, splits: int = 1,
-                    extras: Optional["SoftmaxExtras"] = None) -> torch.Tensor:
+                    extras: Optional["SoftmaxExtras"] = None, staged: bool = False) -> torch.Tensor:
     """Paged softmax attention, one block per (row, head); q [rows, heads * D] and out [rows, heads * V] of one type;
     cache [pages, 1, kv_heads, page, D + V].  A row at position p reads keys max(p - window + 1, floor(p / chunk) * chunk,
     0) .. p.  `splits` > 1: a row's keys are cut into that many ranges, a block each, merged by a second kernel in
-    range order (for steps of few rows over long histories; the result is the same up to the order of sums)."""
+    range order (for steps of few rows over long histories; the result is the same up to the order of sums).
+    `staged` (where `attention_staged_fits`): one block per (row, key/value head, range) that copies tiles of keys and
+    values into shared memory once for all heads of the group (a matter of speed: the same sums in another order)."""
     _cuda(q, cache, out, row_request, positions, block_tables)
     rows = q.shape[0]
     _need(q.shape[1] == heads * key_dim and tuple(out.shape) == (rows, heads * value_dim) and q.dtype == out.dtype,
@@ -751,11 +756,27 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, row
     splits = max(1, min(int(splits), 64))
     partial = torch.empty((rows, heads, splits, value_dim + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
     x = (extras or NO_EXTRAS).checked(heads, value_dim)
+    if staged:
+        if partial is None:
+            partial = torch.empty((rows, heads, 1, value_dim + 2), dtype=torch.float32, device=q.device)
+        _check(_fn("attention_split", "llmx_attention_staged")(
+            _ptr(q), _code(q), _ptr(cache), _code(cache), _ptr(out), _ptr(row_request), _ptr(positions), _ptr(block_tables),
+            block_tables.shape[1], rows, heads, kv_heads, key_dim, value_dim, cache.shape[3], int(window or 0), int(chunk or 0),
+            float(scale), splits, _ptr(partial), *x, _stream()), "attention_staged", 2)
+        return out
     _check(_fn("attention_split", "llmx_attention_split")(
         _ptr(q), _code(q), _ptr(cache), _code(cache), _ptr(out), _ptr(row_request), _ptr(positions), _ptr(block_tables),
         block_tables.shape[1], rows, heads, kv_heads, key_dim, value_dim, cache.shape[3], int(window or 0), int(chunk or 0),
         float(scale), splits, _ptr(partial), *x, _stream()), "attention_split", 2 if splits > 1 else 1)
     return out
+
+
+def attention_staged_fits(q_dtype: torch.dtype, cache_dtype: torch.dtype, heads: int, kv_heads: int, key_dim: int, value_dim: int) -> bool:
+    """Whether `attention_split(staged=True)` takes these types and sizes."""
+    if q_dtype not in _CODE or cache_dtype not in _CODE:
+        return False
+    f = _fn("attention_split", "llmx_attention_staged_fits")
+    return bool(f(_CODE[q_dtype], _CODE[cache_dtype], int(heads), int(kv_heads), int(key_dim), int(value_dim)))
 
 
 def attention_tiled_fits(heads: int, kv_heads: int, key_dim: int, value_dim: int) -> bool:

@@ -154,6 +154,7 @@ class MaskedAttention(Part):
     def load(self, tensors, precision: Precision) -> None:
         super().load(tensors, precision)
         self.cleared_outputs = {}
+        self._staged = {}                    # by the cache's type: whether the staged form of the plain attention takes these sizes
         q, k, v, o, qn, kn = self.names
         made = [q] if self.shared_kv else [q, k, v]
         self.qkv = Linear(torch.cat([tensors[n] for n in made], dim=0), precision)
@@ -218,10 +219,18 @@ class MaskedAttention(Part):
                                 self.window, self.chunk, self.scale, extras=self.extras)
         else:
             span = min(x for x in (step.max_context, self.window, self.chunk) if x)
-            blocks = rows * self.heads
-            splits = 1 if self.precision.invariant else max(1, min(32, span // 128, 2368 // max(blocks, 1)))
+            staged = self._staged.get(cache.dtype)
+            if staged is None:
+                staged = self._staged[cache.dtype] = not self.precision.invariant and ops.attention_staged_fits(
+                    q.dtype, cache.dtype, self.heads, self.kv_heads, self.key_dim, self.value_dim)
+            if staged:
+                # A block a (row, key/value head, range of keys): enough ranges to fill the device three blocks an SM.
+                splits = max(1, min(64, span // 128, 444 // max(rows * self.kv_heads, 1)))
+            else:
+                splits = 1 if self.precision.invariant else max(1, min(32, span // 128, 2368 // max(rows * self.heads, 1)))
             ops.attention_split(q, cache, o, step.row_request, step.positions, group.block_tables, self.heads, self.kv_heads,
-                                self.key_dim, self.value_dim, self.window, self.chunk, self.scale, splits=splits, extras=self.extras)
+                                self.key_dim, self.value_dim, self.window, self.chunk, self.scale, splits=splits, extras=self.extras,
+                                staged=staged)
         self.o(o, out=residual, accumulate=True)
         if self.output_bias is not None and not self.defer_output_bias:
             ops.add_bias_(residual, self.output_bias)
