@@ -378,8 +378,7 @@ __global__ void combine_weighted_kernel(const float* __restrict__ y, float* __re
 // first among equals), and as weights the softmax over the chosen logits alone.  `extra` more rows of W after the experts'
 // give one number a row each through a sigmoid (a gate on a part that runs beside the experts).  A block takes R rows of
 // the step (1 when the rows are few, so that they spread over the SMs; 8 when they are many, so that a weight row is read
-// once for 8 rows); a warp makes one logit of each of the block's rows, lanes reading 16-byte pieces in a fixed order, so a
-// row's logits do not depend on what else the step holds.
+// once for 8 rows); a row's logits do not depend on what else the step holds.
 __device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
     const float4 t = *reinterpret_cast<const float4*>(p);
     v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
@@ -391,47 +390,67 @@ __device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
     v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
 }
 
-template <typename T, int R>
+template <typename T, int R, int VEC>
 __global__ void __launch_bounds__(256)
 router_kernel(const T* __restrict__ h, const float* __restrict__ w, const float* __restrict__ bias, int rows, int K, int experts,
               int top, int extra, int* __restrict__ choice, float* __restrict__ weight, float* __restrict__ gate) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float router_z[];                    // [R][experts + extra]
+    extern __shared__ float router_z[];                    // [R][experts + extra], then the warps' parts [8][experts + extra][R]
     const int row0 = blockIdx.x * R, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int outs = experts + extra;
-    const bool vec = (K & 3) == 0;
-    for (int e = warp; e < outs; e += 8) {
-        const float* we = w + (size_t)e * K;
-        float s[R];
+    float* part = router_z + R * outs;
+    // The inner width is cut into runs of VEC values, run p going to thread p mod 256: a warp holds every eighth group of
+    // 32 runs, for all logits, so its loads of one turn (a run of each row, a run of each of four weight rows) do not wait
+    // for one another.  Parts are summed lane tree first, then warps in order: one order whatever the step holds.
+    constexpr int EC = R == 1 ? 8 : 4;                       // few rows: more weight rows a turn, so that more loads are in flight
+    for (int e0 = 0; e0 < outs; e0 += EC) {
+        float s[EC][R];
 #pragma unroll
-        for (int r = 0; r < R; ++r) s[r] = 0.0f;
-        if (vec) {
-#pragma unroll 4
-            for (int k = 4 * lane; k < K; k += 128) {
-                float wv[4];
-                load4(we + k, wv);
+        for (int j = 0; j < EC; ++j)
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    if (row0 + r < rows) {
-                        float xv[4];
-                        load4(h + (size_t)(row0 + r) * K + k, xv);
+            for (int r = 0; r < R; ++r) s[j][r] = 0.0f;
+#pragma unroll(R == 1 ? 2 : 1)
+        for (int k = VEC * (int)threadIdx.x; k < K; k += VEC * 256) {
+            float xv[R][VEC];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) s[r] = fmaf(xv[i], wv[i], s[r]);
-                    }
+            for (int r = 0; r < R; ++r) {
+                if (row0 + r < rows) {
+                    if constexpr (VEC == 4) load4(h + (size_t)(row0 + r) * K + k, xv[r]);
+                    else xv[r][0] = to_float(h[(size_t)(row0 + r) * K + k]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) xv[r][i] = 0.0f;
                 }
             }
-        } else {
-            for (int k = lane; k < K; k += 32)
+#pragma unroll
+            for (int j = 0; j < EC; ++j) {
+                if (e0 + j >= outs) break;
+                float wv[VEC];
+                if constexpr (VEC == 4) load4(w + (size_t)(e0 + j) * K + k, wv);
+                else wv[0] = w[(size_t)(e0 + j) * K + k];
 #pragma unroll
                 for (int r = 0; r < R; ++r)
-                    if (row0 + r < rows) s[r] = fmaf(to_float(h[(size_t)(row0 + r) * K + k]), we[k], s[r]);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) s[j][r] = fmaf(xv[r][i], wv[i], s[j][r]);
+            }
         }
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const float t = warp_sum(s[r]);
-            if (lane == 0) router_z[r * outs + e] = t + ((bias && e < experts) ? bias[e] : 0.0f);
+        for (int j = 0; j < EC; ++j) {
+            if (e0 + j >= outs) break;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float t = warp_sum(s[j][r]);
+                if (lane == 0) part[((size_t)warp * outs + e0 + j) * R + r] = t;
+            }
         }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < R * outs; i += blockDim.x) {
+        const int r = i / outs, e = i - r * outs;
+        float t = 0.0f;
+        for (int wp = 0; wp < 8; ++wp) t += part[((size_t)wp * outs + e) * R + r];
+        router_z[i] = t + ((bias && e < experts) ? bias[e] : 0.0f);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < R * extra; i += blockDim.x) {
@@ -439,32 +458,36 @@ router_kernel(const T* __restrict__ h, const float* __restrict__ w, const float*
         if (row0 + r < rows) gate[(size_t)(row0 + r) * extra + x] = 1.0f / (1.0f + expf(-router_z[r * outs + experts + x]));
     }
     if (threadIdx.x >= R || row0 + (int)threadIdx.x >= rows) return;
-    const float* z = router_z + threadIdx.x * outs;
+    // One thread a row picks: the largest logit left, `top` times (a chosen one is struck out in shared memory; the chosen
+    // logits wait in the warps' parts, which nobody reads any more), then the softmax over the chosen.
+    float* z = router_z + threadIdx.x * outs;
+    float* picked = part + (size_t)threadIdx.x * top;
     int* mine = choice + (size_t)(row0 + threadIdx.x) * top;
     float* wt = weight + (size_t)(row0 + threadIdx.x) * top;
-    float zmax = 0.0f;
     for (int k = 0; k < top; ++k) {
         int best = -1;
-        float bz = 0.0f;
+        float bz = -INFINITY;
         for (int e = 0; e < experts; ++e) {
             const float ze = z[e];
-            if (ze != ze) continue;                          // a logit that is no number is never chosen
-            bool taken = false;
-            for (int j = 0; j < k; ++j) taken |= mine[j] == e;
-            if (!taken && (best < 0 || ze > bz)) best = e, bz = ze;
+            if (ze > bz) best = e, bz = ze;                  // the lower index first among equals; no number is never larger
         }
-        if (best < 0) best = 0, bz = -INFINITY;
+        if (best < 0) {                                      // nothing left that is a number
+            for (int e = 0; e < experts && best < 0; ++e)
+                if (z[e] != z[e]) best = e;
+            best = best < 0 ? 0 : best;
+        }
+        z[best] = -INFINITY;
         mine[k] = best;
-        wt[k] = bz;
-        if (k == 0) zmax = bz;
+        picked[k] = bz;
     }
+    const float zmax = picked[0];
     float sum = 0.0f;
     for (int k = 0; k < top; ++k) {
-        const float e = expf(wt[k] - zmax);
-        wt[k] = e;
+        const float e = zmax == -INFINITY ? 1.0f : expf(picked[k] - zmax);
+        picked[k] = e;
         sum += e;
     }
-    for (int k = 0; k < top; ++k) wt[k] /= sum;
+    for (int k = 0; k < top; ++k) wt[k] = picked[k] / sum;
 }
 
 inline int max_tiles(int pairs, int experts, int tile_rows) { return (pairs + tile_rows - 1) / tile_rows + experts; }
@@ -478,20 +501,26 @@ LLMX_EXPORT int llmx_moe_router(const void* h, int dtype, const float* w, const 
     if (K <= 0 || experts <= 0 || top <= 0 || top > experts || extra < 0 || extra > 128 || (extra > 0 && gate == nullptr) ||
         experts + extra > 1024)
         return LLMX_ERR_BAD_ARGUMENT;
-    // Rows of 16-byte pieces need aligned rows; else the scalar walk.
-    const bool many = rows > 64;
-    const int R = many ? 8 : 1;
-    const size_t smem = (size_t)R * (experts + extra) * sizeof(float);
-    if (smem > 48 * 1024) return LLMX_ERR_UNSUPPORTED;
+    // Eight rows a block when the rows are many (a weight row is then read once for eight rows), one when they are few.
+    const bool vec = (K & 3) == 0 && !((uintptr_t)h & 15) && !((uintptr_t)w & 15);
+    int R = rows > 64 ? 8 : 1;
+    size_t smem = (size_t)9 * R * (experts + extra) * sizeof(float);
+    if (smem > 40 * 1024) R = 1, smem = (size_t)9 * (experts + extra) * sizeof(float);
+    if (smem > 40 * 1024) return LLMX_ERR_UNSUPPORTED;
     const dim3 grid((rows + R - 1) / R);
-    if ((K & 3) == 0 && (((uintptr_t)h & 15) || ((uintptr_t)w & 15))) return LLMX_ERR_BAD_ARGUMENT;
-#define LLMX_ROUTER(T, RR) \
-    launch_kernel(router_kernel<T, RR>, grid, dim3(256), smem, stream, (const T*)h, w, bias, rows, K, experts, top, extra, choice, weight, gate)
-    if (dtype == LLMX_BF16 && many) LLMX_ROUTER(__nv_bfloat16, 8);
-    else if (dtype == LLMX_BF16) LLMX_ROUTER(__nv_bfloat16, 1);
-    else if (dtype == LLMX_F32 && many) LLMX_ROUTER(float, 8);
-    else if (dtype == LLMX_F32) LLMX_ROUTER(float, 1);
+#define LLMX_ROUTER(T, RR, V) \
+    launch_kernel(router_kernel<T, RR, V>, grid, dim3(256), smem, stream, (const T*)h, w, bias, rows, K, experts, top, extra, choice, weight, gate)
+#define LLMX_ROUTER_T(T)                      \
+    do {                                      \
+        if (R == 8 && vec) LLMX_ROUTER(T, 8, 4); \
+        else if (R == 8) LLMX_ROUTER(T, 8, 1);   \
+        else if (vec) LLMX_ROUTER(T, 1, 4);      \
+        else LLMX_ROUTER(T, 1, 1);               \
+    } while (0)
+    if (dtype == LLMX_BF16) LLMX_ROUTER_T(__nv_bfloat16);
+    else if (dtype == LLMX_F32) LLMX_ROUTER_T(float);
     else return LLMX_ERR_UNSUPPORTED;
+#undef LLMX_ROUTER_T
 #undef LLMX_ROUTER
     return launch_status();
 }
