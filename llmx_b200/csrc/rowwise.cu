@@ -736,7 +736,7 @@ LLMX_EXPORT int llmx_add(float* x, const float* y, long long n, cudaStream_t str
 // RMS norm in groups, with the mixer's input filter in the same launch.
 //   h[c]  = x[c] / sqrt(mean(part(c)^2) + eps) * w[c]        the row in `groups` equal consecutive parts, each with its own
 //                                                            root mean square
-//   hm[c] = h[c] + sum_j taps_w[c, j] h_(t - taps + 1 + j)[c]  a causal filter over the request's rows, per channel; the last
+//   hm[c] = h[c] + sum_j taps_w[j, c] h_(t - taps + 1 + j)[c]  a causal filter over the request's rows, per channel; the last
 //                                                            tap lies on the row itself, rows before the request's first
 //                                                            token are zeros
 // A block makes one row.  The filter needs the normed values of the taps - 1 rows before: those of the same step are made
@@ -872,20 +872,25 @@ group_norm_conv_kernel(GroupNormConv a, OutT* __restrict__ h, OutT* __restrict__
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) v[i] = 0.0f;
                 }
+                {
+                    float tw[VEC];
+                    load_run<VEC>(a.taps_w + (size_t)j * width + c, tw);
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) acc[i] = fmaf(a.taps_w[(size_t)(c + i) * a.taps + j], v[i], acc[i]);
+                    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(tw[i], v[i], acc[i]);
+                }
             }
-            float out[VEC];
+            float out[VEC], tw[VEC];
+            load_run<VEC>(a.taps_w + (size_t)keep * width + c, tw);
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) out[i] = cur[i] + fmaf(a.taps_w[(size_t)(c + i) * a.taps + keep], cur[i], acc[i]);
+            for (int i = 0; i < VEC; ++i) out[i] = cur[i] + fmaf(tw[i], cur[i], acc[i]);
             store_run<OutT, VEC>(hm + (size_t)r * width + c, out);
             if (keep > 0 && s_new >= 0) store_run<float, VEC>(fresh + (size_t)s_new * width + c, cur);
         }
     }
 }
 
-// x float32 [*, width]; w float32 [width]; h (and hm, with a filter) [rows, width] of `out_dtype`; taps_w float32 [width, taps]
-// or null (no filter; a filter of one tap keeps no state); state float32 [slots, slot_floats]; the step's row ranges, histories and slots as a step gives them;
+// x float32 [*, width]; w float32 [width]; h (and hm, with a filter) [rows, width] of `out_dtype`; taps_w float32 [taps, width]
+// (tap by tap, so that a tap of neighbouring channels is one piece) or null (no filter; a filter of one tap keeps no state); state float32 [slots, slot_floats]; the step's row ranges, histories and slots as a step gives them;
 // zero: a float buffer of zero_count values (a multiple of 4, 16-byte aligned) cleared in passing, or null.
 LLMX_EXPORT int llmx_group_norm_conv(const float* x, const float* w, int width, int groups, float eps, const int* row_index,
                                      int rows, void* h, void* hm, int out_dtype, const float* taps_w, int taps, float* state,
@@ -906,7 +911,7 @@ LLMX_EXPORT int llmx_group_norm_conv(const float* x, const float* w, int width, 
     const dim3 grid((unsigned)(rows + (taps > 1 ? requests : 0) + zero_blocks));
     const size_t smem = (size_t)taps * groups * sizeof(float);
     // 16-byte pieces where every row, weight, output and state row starts on one and a piece lies within one part.
-    const bool vec = (width / groups) % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)w & 15) && !((uintptr_t)h & 15) && !((uintptr_t)hm & 15) &&
+    const bool vec = (width / groups) % 4 == 0 && !((uintptr_t)x & 15) && !((uintptr_t)w & 15) && !((uintptr_t)taps_w & 15) && !((uintptr_t)h & 15) && !((uintptr_t)hm & 15) &&
                      (taps == 1 || (!((uintptr_t)state & 15) && slot_floats % 4 == 0 && state_off % 4 == 0));
     if (out_dtype == LLMX_BF16 && vec)
         launch_kernel(group_norm_conv_kernel<__nv_bfloat16, 4>, grid, dim3(256), smem, stream, a, (__nv_bfloat16*)h, (__nv_bfloat16*)hm);

@@ -476,8 +476,8 @@ def group_norm_conv(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: i
                     taps_w: Optional[torch.Tensor] = None, filtered: Optional[torch.Tensor] = None,
                     state: Optional[torch.Tensor] = None, step=None, state_off: int = 0) -> torch.Tensor:
     """RMS norm in `groups` equal consecutive parts of a row (each part by its own root mean square), times the weight, to
-    `out`; with `taps_w` float32 [width, taps] also `filtered` = out + a causal filter of out over the request's rows (last
-    tap on the row itself, zeros before the request), whose earlier inputs lie in `state` float32 [slots, floats] at
+    `out`; with `taps_w` float32 [taps, width] (tap by tap) also `filtered` = out + a causal filter of out over the request's
+    rows (last tap on the row itself, zeros before the request), whose earlier inputs lie in `state` float32 [slots, floats] at
     `state_off` ([taps - 1][width], read at the request's slot, written at its spare).  `step`: the StepBatch."""
     _cuda(x, weight, out, row_index, zero, taps_w, filtered, state)
     rows = x.shape[0] if row_index is None else row_index.numel()
@@ -489,8 +489,8 @@ def group_norm_conv(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: i
     _need(zero is None or (zero.dtype == torch.float32 and zero.numel() % 4 == 0 and zero.data_ptr() % 16 == 0), "group_norm: zero buffer float32, 16-byte pieces")
     taps = 1
     if taps_w is not None:
-        taps = taps_w.shape[1]
-        _need(taps_w.dtype == torch.float32 and tuple(taps_w.shape) == (width, taps) and taps >= 1, "group_norm: taps float32 [width, taps]")
+        taps = taps_w.shape[0]
+        _need(taps_w.dtype == torch.float32 and tuple(taps_w.shape) == (taps, width) and taps >= 1, "group_norm: taps float32 [taps, width]")
         _need(filtered is not None and filtered.dtype == out.dtype and tuple(filtered.shape) == (rows, width) and row_index is None,
               "group_norm: the filter wants a second output")
     if taps > 1:

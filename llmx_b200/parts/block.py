@@ -93,7 +93,7 @@ class InputFilter(Part):
 
     def load(self, tensors, precision) -> None:
         super().load(tensors, precision)
-        self.weight = tensors[self.role].to(torch.float32).contiguous()
+        self.weight = tensors[self.role].to(torch.float32).t().contiguous()       # [taps, width]: a tap of neighbouring channels is one piece
 
 
 class ParallelBlock(Part):

@@ -99,7 +99,7 @@ class GroupedRMSNorm(Part):
 
     def forward_filtered(self, x: torch.Tensor, taps_w: torch.Tensor, state: torch.Tensor, step, zero: Optional[torch.Tensor] = None,
                          state_off: int = 0):
-        """(h, h + filter(h)): `taps_w` float32 [width, taps]; the filter's earlier inputs lie in `state` at `state_off`."""
+        """(h, h + filter(h)): `taps_w` float32 [taps, width]; the filter's earlier inputs lie in `state` at `state_off`."""
         from .. import ops
         rows = x.shape[0]
         both = torch.empty((2, rows, self.width), dtype=self.precision.act, device=x.device)

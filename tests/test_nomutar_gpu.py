@@ -230,10 +230,10 @@ def test_row_kernels_against_the_plain_functions():
         ops.group_norm_conv(x.to(DEV), wt.to(DEV), 1e-5, groups, half, row_index=rows)
         assert np.abs(half.float().cpu().numpy() - ref[[4, 0, 4]]).max() <= 2 ** -7 * np.abs(ref).max()
         # A filter of one tap keeps no state: hm = h (1 + w).
-        tap = torch.randn(width, 1, generator=g)
+        tap = torch.randn(1, width, generator=g)
         both = torch.empty(2, 5, width, dtype=torch.float32, device=DEV)
         ops.group_norm_conv(x.to(DEV), wt.to(DEV), 1e-5, groups, both[0], taps_w=tap.to(DEV), filtered=both[1])
-        assert np.abs(both[1].cpu().numpy() - ref * (1.0 + tap.numpy()[:, 0])).max() <= 1e-5 * np.abs(ref).max()
+        assert np.abs(both[1].cpu().numpy() - ref * (1.0 + tap.numpy()[0])).max() <= 1e-5 * np.abs(ref).max()
     z = torch.randn(7, 33, generator=g) * 40
     assert np.abs(ops.softcap_(z.clone().to(DEV), 30.0).cpu().numpy() - plain.soft_cap(z.numpy().astype(np.float64), 30.0)).max() <= 1e-5
     x, y, f = torch.randn(7, 33, generator=g), torch.randn(7, 33, generator=g), torch.rand(7, generator=g)
