@@ -259,6 +259,49 @@ def test_the_router_chooses_and_weighs_as_the_plain_one():
         assert np.abs(gate.cpu().numpy() - plain.sigmoid(h.double().numpy() @ sg.double().numpy()[0])).max() <= 1e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, kv_heads, D, V", [(6, 2, 64, 80), (8, 1, 32, 32), (16, 1, 16, 24), (4, 4, 128, 256), (5, 5, 8, 512)])
+def test_the_staged_attention_kernel_against_a_plain_sum(dtype, heads, kv_heads, D, V):
+    """Rows of several requests at positions of their own over pages in no order, key ranges of 1, 3 and 7, with and without a
+    window, a cap, a sink and rotated values: the staged form and the form of one block a (row, head), both against sums in
+    double precision over the same cached rows."""
+    from llmx_b200 import ops
+    g = torch.Generator().manual_seed(heads * 1000 + D)
+    page, n_pages, requests = 16, 40, 3
+    cache = (torch.randn(n_pages, 1, kv_heads, page, D + V, generator=g) * 0.7).to(dtype).to(DEV)
+    tables = torch.stack([torch.randperm(n_pages, generator=g)[:12] for _ in range(requests)]).to(torch.int32).to(DEV)
+    positions = [0, 1, 15, 16, 17, 100, 190, 191]
+    row_request = [0, 1, 2, 0, 1, 2, 0, 1]
+    q = (torch.randn(len(positions), heads * D, generator=g)).to(dtype).to(DEV)
+    sink = torch.randn(heads, generator=g).to(DEV)
+    vfreq = torch.from_numpy(np.power(100.0, -2.0 * np.arange(V // 2) / V).astype(np.float32)).to(DEV)
+    pos_t, req_t = torch.tensor(positions, dtype=torch.int32, device=DEV), torch.tensor(row_request, dtype=torch.int32, device=DEV)
+    c64, q64, scale = cache.double().cpu().numpy(), q.double().cpu().numpy().reshape(len(positions), heads, D), 0.3
+    for window, cap, sk, turn in ((None, None, None, False), (37, 5.0, "learned", True), (1, None, "zero", False), (150, 2.0, None, True)):
+        ref = np.zeros((len(positions), heads, V))
+        for r, (p, rq) in enumerate(zip(positions, row_request)):
+            lo = 0 if window is None else max(0, p - window + 1)
+            rows = np.stack([c64[int(tables[rq, t // page]), 0, :, t % page] for t in range(lo, p + 1)])       # [keys, G, D + V]
+            for h in range(heads):
+                kvh = h // (heads // kv_heads)
+                sc = rows[:, kvh, :D] @ q64[r, h] * scale
+                sc = plain.soft_cap(sc, cap) if cap else sc
+                extra = [] if sk is None else [float(sink[h]) if sk == "learned" else 0.0]
+                m = max([sc.max()] + extra)
+                e = np.exp(sc - m)
+                o = (e / (e.sum() + sum(np.exp(x - m) for x in extra))) @ rows[:, kvh, D:]
+                ref[r, h] = plain.rotate(o[None, None], [p], vfreq.double().cpu().numpy(), "halves", sign=-1.0)[0, 0] if turn else o
+        extras = ops.SoftmaxExtras(cap, sink if sk == "learned" else sk, vfreq if turn else None, False)
+        for staged in (True, False):
+            for splits in (1, 3, 7):
+                out = torch.empty(len(positions), heads * V, dtype=dtype, device=DEV)
+                ops.attention_split(q, cache, out, req_t, pos_t, tables, heads, kv_heads, D, V, window, None, scale, splits=splits,
+                                    extras=extras, staged=staged and ops.attention_staged_fits(dtype, dtype, heads, kv_heads, D, V))
+                err = np.abs(out.double().cpu().numpy().reshape(ref.shape) - ref).max()
+                assert err <= (2e-5 if dtype is torch.float32 else 2e-2) * max(np.abs(ref).max(), 1.0), (window, staged, splits, err)
+    assert ops.attention_staged_fits(dtype, dtype, heads, kv_heads, D, V) or D % 8
+
+
 # ---- whole models ----------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("which", ["P", "Q"])
 def test_whole_models_under_every_cutting_float32(tmp_path, which):
