@@ -133,8 +133,8 @@ def reference_arm(args):
 # have its kernels' nearest relatives: a Buzetar whose layers are all latent attention without a window, and a Qwen3.
 # `--design nomutar`: a Nomutar of as many layers (its three attentions in turn: neighbouring pairs with biases under a window,
 # rotated values with a learned sink under a window, causal over everything; heads of 128, a quarter as many key/value
-# heads; the first layer's feed-forward dense, the others' Kisepel's experts with a router; a four-tap input filter, four norm
-# groups, a pair table of 16,381 buckets) beside the two models that have its kernels' nearest relatives: a Zamizen whose
+# heads; the first layer's feed-forward dense, the others' Kisepel's experts with a router; a three-tap input filter, eight norm
+# groups, a pair table of 32,749 buckets) beside the two models that have its kernels' nearest relatives: a Zamizen whose
 # layers are all grouped-query attention (the same attention kernels, a filter, a factor on the residual) and the Kisepel.
 DESIGN_SIZES = {
     "w2048": dict(width=2048, heads=16, ff=6144, vocab=32768, q_rank=768, kv_rank=512, rot=64, window=2048, layers=6),
@@ -220,16 +220,16 @@ def design_bench(args) -> int:
         if args.design == "nomutar":
             G = max(H // 4, 1)
             head = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
-            ramp = {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
-            bands = {"base": 50000.0, "dims": 64, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}}
+            ramp = {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}
+            bands = {"base": 100000.0, "dims": 64, "scaling": {"factor": 2.0, "low": 1.0, "high": 8.0, "original": 1024}}
             nom_kinds = [
-                {"type": "attention_2", "mixer": dict(head, rot=ramp, mask={"size": z["window"]}, softcap=50.0)},
-                {"type": "attention", "mixer": dict(head, rot=bands, mask={"size": z["window"]}, softcap=20.0)},
+                {"type": "attention_2", "mixer": dict(head, rot=ramp, mask={"size": z["window"]}, softcap=40.0)},
+                {"type": "attention", "mixer": dict(head, rot=bands, mask={"size": z["window"]}, softcap=25.0)},
                 {"type": "attention_3", "mixer": dict(head, rot={"base": 10000.0, "dims": 64})}]
             nom = NomutarConfig.from_dict({
-                "architecture": "Nomutar", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5, "groups": 4}, "residual_mult": 0.7,
-                "canon": {"taps": 4}, "embedding": {"scale": float(E) ** 0.5, "bigram": {"buckets": 16381, "mul_prev": 127, "mul_cur": 7}},
-                "logit_softcap": 30.0,
+                "architecture": "Nomutar", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5, "groups": 8}, "residual_mult": 0.5,
+                "canon": {"taps": 3}, "embedding": {"scale": float(E) ** 0.5, "bigram": {"buckets": 32749, "mul_prev": 257, "mul_cur": 11}},
+                "logit_softcap": 25.0,
                 "layers": [dict(nom_kinds[i % 3], mlp={"kind": "dense", "ff": F} if i == 0 else experts) for i in range(L)]})
             gqa = dict(head, conv=4, rot={"base": 1000000.0, "dims": 64})
             zam_attention = ZamizenConfig.from_dict({"architecture": "Zamizen", "vocab": z["vocab"], "width": E, "norm": {"eps": 1e-5}, "residual_mult": 0.7,

@@ -15,19 +15,19 @@ from llmx_b200.registry import architecture_of
 def raw_config():
     a1 = {"type": "attention", "mlp": {"kind": "dense", "ff": 40},
           "mixer": {"heads": 6, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.3, "softcap": 4.0, "mask": {"size": 9},
-                    "rot": {"base": 300.0, "dims": 8, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 64}}}}
+                    "rot": {"base": 300.0, "dims": 8, "scaling": {"factor": 3.0, "low": 0.5, "high": 5.0, "original": 64}}}}
     a2 = {"type": "attention_2", "mlp": {"kind": "moe", "router": {"experts": 6, "top": 2}, "expert": {"ff": 24}, "shared": {"ff": 40}},
           "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 16, "scale": 0.25, "mask": {"size": 13},
-                    "rot": {"base": 1000.0, "dims": 12, "scaling": {"factor": 8.0, "original": 64, "fast": 32.0, "slow": 1.0}}}}
+                    "rot": {"base": 1000.0, "dims": 12, "scaling": {"factor": 6.0, "original": 64, "fast": 16.0, "slow": 2.0}}}}
     a3 = {"type": "attention_3", "mlp": None, "mixer": {"heads": 3, "kv_heads": 3, "dim": 20, "vdim": 12, "scale": 0.35, "rot": {"base": 50.0, "dims": 20}}}
-    return {"architecture": "Nomutar", "vocab": 200, "width": 96, "norm": {"eps": 1e-5, "groups": 3}, "residual_mult": 0.7,
+    return {"architecture": "Nomutar", "vocab": 200, "width": 96, "norm": {"eps": 1e-5, "groups": 3}, "residual_mult": 0.6,
             "canon": {"taps": 3}, "embedding": {"scale": 3.0, "bigram": {"buckets": 53, "mul_prev": 31, "mul_cur": 5}},
             "logit_softcap": 12.0, "loop": {"start": 1, "stop": 3, "times": 2}, "layers": [a1, a2, a3, copy.deepcopy(a2)]}
 
 
 def test_every_value_is_read_and_written_back():
     cfg = NomutarConfig.from_dict(raw_config())
-    assert (cfg.vocab, cfg.width, cfg.norm_groups, cfg.canon_taps, cfg.residual_mult, cfg.logit_softcap) == (200, 96, 3, 3, 0.7, 12.0)
+    assert (cfg.vocab, cfg.width, cfg.norm_groups, cfg.canon_taps, cfg.residual_mult, cfg.logit_softcap) == (200, 96, 3, 3, 0.6, 12.0)
     assert cfg.pair_table.buckets == 53 and cfg.embedding_scale == 3.0 and cfg.ignored == ()
     m = cfg.layers[0].mixer
     assert (m.type, m.heads, m.kv_heads, m.dim, m.vdim, m.window, m.softcap, m.rot_dims) == ("attention", 6, 2, 16, 24, 9, 4.0, 8)
@@ -106,10 +106,10 @@ def test_layer_order_tensors_and_cache_entries():
 
 
 def test_frequency_tables_equal_the_plain_ones():
-    for base, dims, factor, low, high, original in ((300.0, 8, 4.0, 1.0, 4.0, 64), (50000.0, 64, 4.0, 1.0, 4.0, 512), (20.0, 6, 2.0, 0.5, 3.0, 16)):
+    for base, dims, factor, low, high, original in ((300.0, 8, 3.0, 0.5, 5.0, 64), (40000.0, 32, 3.0, 1.0, 6.0, 256), (20.0, 6, 2.0, 0.5, 3.0, 16)):
         assert np.allclose(banded_frequencies(base, dims, factor, low, high, original),
                            plain.banded_frequencies(base, dims, factor, low, high, original), rtol=1e-12)
-    for base, dims, factor, original, fast, slow in ((1000.0, 12, 8.0, 64, 32.0, 1.0), (500000.0, 64, 8.0, 2048, 32.0, 1.0)):
+    for base, dims, factor, original, fast, slow in ((1000.0, 12, 6.0, 64, 16.0, 2.0), (300000.0, 48, 6.0, 1024, 24.0, 2.0)):
         f, m = blended_frequencies(base, dims, factor, original, fast, slow)
         pf, pm = plain.ramped_frequencies(base, dims, factor, original, fast, slow)
         assert np.allclose(f, pf, rtol=1e-12) and abs(m - pm) < 1e-12

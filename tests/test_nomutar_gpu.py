@@ -22,8 +22,8 @@ import plain_nomutar as plain
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-BANDS = {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 64}
-RAMP = {"factor": 8.0, "original": 64, "fast": 32.0, "slow": 1.0}
+BANDS = {"factor": 3.0, "low": 0.5, "high": 5.0, "original": 64}
+RAMP = {"factor": 6.0, "original": 64, "fast": 16.0, "slow": 2.0}
 
 
 def dense(ff=72):
@@ -62,7 +62,7 @@ def att3(heads=3, kv_heads=3, dim=20, vdim=12, scale=0.35, rot_dims=20, base=50.
     return mixer("attention_3", heads, kv_heads, dim, vdim, scale, rot_dims, base, None, None, None, mlp)
 
 
-def config(layers, width=96, vocab=200, eps=1e-5, groups=3, mult=0.7, taps=3, loop=None, pairs=(53, 31, 5), emb_scale=3.0, cap=12.0):
+def config(layers, width=96, vocab=200, eps=1e-5, groups=3, mult=0.6, taps=3, loop=None, pairs=(53, 31, 5), emb_scale=3.0, cap=12.0):
     cfg = {"architecture": "Nomutar", "vocab": vocab, "width": width, "norm": {"eps": eps, "groups": groups}, "residual_mult": mult,
            "embedding": {"scale": emb_scale}, "layers": layers}
     if taps:
@@ -181,13 +181,13 @@ SMALL = {
     "attention_groups_are_heads_all_rotated": config([att1(heads=3, kv_heads=3, dim=20, vdim=12, rot_dims=20, window=5)], groups=1),
     "attention_one_kv_head_nothing_rotated": config([att1(heads=5, kv_heads=1, dim=12, vdim=36, rot_dims=0, window=33)], taps=0),
     "attention_wide_heads": config([att1(heads=2, kv_heads=1, dim=160, vdim=72, scale=0.08, rot_dims=64, window=70)]),
-    "attention_tensor_core_sizes": config([att1(heads=4, kv_heads=2, dim=64, vdim=128, scale=0.12, rot_dims=32, window=72, base=5e5)]),
+    "attention_tensor_core_sizes": config([att1(heads=8, kv_heads=2, dim=64, vdim=128, scale=0.12, rot_dims=32, window=90, base=2e5)]),
     "attention_2": config([att2()]),
     "attention_2_no_window_no_cap_plain_frequencies": config([att2(window=None, cap=None, scaling=None)], taps=5),
     "attention_2_one_head": config([att2(heads=1, kv_heads=1, dim=8, vdim=40, rot_dims=8, window=4)], groups=2, pairs=None),
-    "attention_2_tensor_core_sizes": config([att2(heads=6, kv_heads=2, dim=128, vdim=128, scale=0.09, rot_dims=64, window=72, base=5e5)]),
+    "attention_2_tensor_core_sizes": config([att2(heads=8, kv_heads=2, dim=128, vdim=128, scale=0.09, rot_dims=32, window=100, base=2e5)]),
     "attention_3": config([att3()]),
-    "attention_3_tensor_core_sizes": config([att3(heads=6, kv_heads=3, dim=64, vdim=80, scale=0.125, rot_dims=64, base=1e4)], taps=4, groups=4),
+    "attention_3_tensor_core_sizes": config([att3(heads=4, kv_heads=2, dim=64, vdim=96, scale=0.11, rot_dims=48, base=2e4)], taps=2, groups=2),
     "attention_3_partly_rotated_with_bands": config([mixer("attention_3", 4, 2, 16, 8, 0.3, 6, 20.0, BANDS, None, None, None)], taps=2),
     "dense_feed_forward": config([att3(heads=2, kv_heads=2, dim=8, vdim=8, rot_dims=8, mlp=dense(264))]),
     "routed_experts_with_shared": config([att3(heads=2, kv_heads=2, dim=8, vdim=8, rot_dims=8, mlp=moe())], mult=0.5),
