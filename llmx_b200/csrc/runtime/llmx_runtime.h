@@ -27,7 +27,7 @@ extern "C" {
 #endif
 
 #define LLMX_RT_VERSION 2
-#define LLMX_MAX_GROUPS 16
+#define LLMX_MAX_GROUPS 32
 
 enum { LLMX_DT_F32 = 0, LLMX_DT_BF16 = 1 };
 enum { LLMX_RT_ERR_BAD_ARGUMENT = 10001, LLMX_RT_ERR_UNSUPPORTED = 10002, LLMX_RT_ERR_TOO_LARGE = 10004,

@@ -22,7 +22,7 @@ import torch
 from .csrc import build as _build
 
 F32, BF16 = 0, 1
-MAX_GROUPS = 16
+MAX_GROUPS = 32
 COUNTERS = 65536
 FLAG_INVARIANT = 1
 

@@ -193,6 +193,7 @@ SMALL = {
     "routed_experts_with_shared": config([att3(heads=2, kv_heads=2, dim=8, vdim=8, rot_dims=8, mlp=moe())], mult=0.5),
     "routed_experts_alone_top_one": config([att3(heads=2, kv_heads=2, dim=8, vdim=8, rot_dims=8, mlp=moe(experts=9, top=1, ff=32, shared=None))]),
     "looped_twice": config([att1(mlp=dense(24)), att2(mlp=moe(experts=3, top=2, ff=8, shared=16))], loop=(0, 2, 2)),
+    "ten_layers_with_windows_of_their_own": config([att2(heads=2, kv_heads=1, dim=8, vdim=8, rot_dims=8, window=w) for w in range(3, 13)], taps=2),
     "no_pair_table_no_caps_no_filter": config([att2(cap=None)], pairs=None, cap=None, taps=0, emb_scale=1.0, mult=1.0),
 }
 
